@@ -1,0 +1,161 @@
+/* ttb.h -- C ABI of the B200 (sm_100a) matmul backend for tinytensor.
+ *
+ * Every entry point takes plain pointers and sizes; nothing here depends on
+ * tinytensor, torch or C++.  The library (libttb.so) is what a tinytensor
+ * build links in place of its CUDA matmul translation unit
+ * (tinytensor/tensor/backend/cuda/matmul.cu); the C++ shim that adapts
+ * `Tensor` to these calls lives in tinytensor_b200/csrc/tt_runner_shim.cu.
+ *
+ * Naming follows the reference: lhs[B,N,K] . rhs[B,K,M] -> out[B,N,M]
+ * (tinytensor/autograd/binary_ops.cpp:162-164).
+ */
+#ifndef TTB_H_
+#define TTB_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TTB_API __attribute__((visibility("default")))
+#else
+#define TTB_API
+#endif
+
+/* Element types.  Values equal tinytensor::ScalarType (include/tt/scalar.h:21-29)
+ * so the shim can pass `static_cast<int>(tensor.dtype())` straight through.
+ * bool8 (0) never reaches the backend (tinytensor/tensor/tensor.cpp:2395-2397)
+ * and is rejected with TTB_EDTYPE. */
+enum ttb_dtype {
+    TTB_BOOL8 = 0,
+    TTB_U8 = 1,
+    TTB_I16 = 2,
+    TTB_I32 = 3,
+    TTB_I64 = 4,
+    TTB_F32 = 5,
+    TTB_F64 = 6
+};
+
+/* Status codes.  0 is success; negatives are errors with a message in
+ * ttb_last_error().  The reference throws TTException for user errors
+ * (include/tt/exception.h:15-25) and exits on launch failure
+ * (backend/cuda/kernel_launch.cuh:25-28); the shim maps any non-zero status to
+ * TT_EXCEPTION. */
+enum ttb_status {
+    TTB_OK = 0,
+    TTB_EINVAL = -1,       /* null pointer, negative stride/offset, bad option */
+    TTB_ESHAPE = -2,       /* rank/inner-dim/batch mismatch, size < 1, overflow */
+    TTB_EDTYPE = -3,       /* bool8 or unknown dtype */
+    TTB_EDEVICE = -4,      /* device id out of range */
+    TTB_ECUDA = -5,        /* a CUDA runtime/driver call failed */
+    TTB_ETIMEOUT = -6,     /* a bounded device-side wait gave up */
+    TTB_ENOMEM = -7,       /* workspace allocation failed */
+    TTB_EUNSUPPORTED = -8, /* forced kernel variant cannot take these views */
+    TTB_ELIMIT = -9        /* size beyond a documented fixed limit */
+};
+
+/* A strided rank-3 view, exactly the fields tinytensor's Tensor carries
+ * (include/tt/tensor.h:1570-1577): element offset into the storage, shape and
+ * element strides (0 allowed, negative never -- tinytensor/tensor/index.cpp:21-25).
+ * `data` is the storage base (DeviceMemory<T>::data_ptr(),
+ * backend/cuda/matmul.cu:54-57); the first element is data + offset. */
+typedef struct ttb_view {
+    const void *data;
+    int64_t offset;
+    int64_t size[3];
+    int64_t stride[3];
+} ttb_view;
+
+/* Kernel variants, reported by ttb_last_variant() and forced by the
+ * "force_variant" option. */
+enum ttb_variant {
+    TTB_VARIANT_AUTO = 0,
+    TTB_VARIANT_SIMT = 1,         /* CUDA-core register-tiled kernel, any dtype/stride */
+    TTB_VARIANT_TCGEN05_3XTF32 = 2, /* f32: tcgen05 + TMEM + TMA, split-TF32 */
+    TTB_VARIANT_DMMA_F64 = 3,     /* f64: FP64 tensor-core (DMMA) kernel */
+    TTB_VARIANT_SIMT_SPLITK = 4,  /* SIMT with K split over CTAs + scratch reduce */
+    TTB_VARIANT_TCGEN05_2CTA = 5  /* f32: tcgen05 cta_group::2 (CTA pairs) */
+};
+
+/* ---- the hot path -------------------------------------------------------
+ *
+ * ttb_batched_matmul: out[b] = lhs[b] . rhs[b] on device `device_id`, queued
+ * on `stream` (a cudaStream_t; NULL = the legacy default stream, which is what
+ * the reference launches on, backend/cuda/kernel_launch.cuh:24).  All pointers
+ * are device pointers.  `out` receives a contiguous row-major [B,N,M] result
+ * with offset 0, the layout the reference allocates (backend/cuda/matmul.cu:50,74).
+ * Views may be arbitrarily strided; no contiguous copy is made.
+ * Replaces: tinytensor::cuda::batched_matmul_runner's contiguous()+launch
+ * (backend/cuda/matmul.cu:26-78) and matmul_kernel<T>
+ * (backend/cuda/kernel/matmul.cuh:27-151).
+ * Does not synchronise (neither does the reference). */
+TTB_API int ttb_batched_matmul(const ttb_view *lhs, const ttb_view *rhs, void *out,
+                               int dtype, int device_id, void *stream);
+
+/* Same product, but the result goes to a strided destination
+ * out[b*out_stride[0] + i*out_stride[1] + j*out_stride[2]] (+ out_offset).
+ * Used by the multi-GPU partitioner to write an output-column block straight
+ * into its place in the full row-major C.  No counterpart in the reference
+ * (its output is always fresh and contiguous). */
+TTB_API int ttb_batched_matmul_strided_out(const ttb_view *lhs, const ttb_view *rhs,
+                                           void *out, int64_t out_offset,
+                                           const int64_t out_stride[3], int dtype,
+                                           int device_id, void *stream);
+
+/* Host-buffer form: lhs/rhs `data` and `out` are HOST pointers (pinned memory
+ * makes the copies asynchronous).  Copies the operands' storage spans to the
+ * device, runs ttb_batched_matmul on `device_id`, copies the contiguous result
+ * back and synchronises.  Device staging buffers are cached per device and
+ * grown on demand.  This is the call a CPU-resident caller makes, the
+ * equivalent of tinytensor's `matmul(a.to(cuda), b.to(cuda)).to(cpu)`
+ * (autograd/unary_ops.cpp:67-83 + backend/cuda/matmul.cu:26-78). */
+TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, void *out,
+                                    int dtype, int device_id);
+
+/* ---- multi-GPU partitioner (host logic only; no communication) ----------
+ *
+ * Splits lhs[B,N,K].rhs[B,K,M] over `world` GPUs the way the partitioner
+ * does: B > 1 -> contiguous batch ranges (no exchange step); B == 1 ->
+ * output-column blocks of rhs/out rounded to `col_align` columns (an
+ * all-gather of C follows).  Writes this rank's half-open range to
+ * [*begin, *end) and returns 0 for batch sharding, 1 for column sharding,
+ * or a negative status.  Ranks past the end of the work get an empty range.
+ * No counterpart in the reference (single-device matmul only). */
+TTB_API int ttb_partition(int64_t B, int64_t N, int64_t K, int64_t M, int world, int rank,
+                          int64_t col_align, int64_t *begin, int64_t *end);
+
+/* ---- introspection / control ------------------------------------------- */
+
+/* Message of the last failing call on this thread ("" if none). */
+TTB_API const char *ttb_last_error(void);
+/* Variant the last successful ttb_batched_matmul on this thread launched. */
+TTB_API int ttb_last_variant(void);
+/* Number of kernels this library has launched on this thread since load. */
+TTB_API int64_t ttb_launch_count(void);
+TTB_API const char *ttb_variant_name(int variant);
+/* Options: "force_variant" (enum ttb_variant; AUTO restores dispatch),
+ * "tf32_terms" (3 = split-TF32, default; 1 = single TF32 pass, test only),
+ * "k_chunk" (k-blocks accumulated inside the tensor core before the partial
+ * sum is folded into fp32 registers; 0 = whole K). Returns TTB_EINVAL for an
+ * unknown key or value. */
+TTB_API int ttb_set_option(const char *key, int64_t value);
+TTB_API int64_t ttb_get_option(const char *key);
+/* Number of visible CUDA devices, or a negative status. */
+TTB_API int ttb_device_count(void);
+/* Reads and clears the device-side error word of `device_id` (set when a
+ * bounded wait inside a kernel gave up).  Synchronises the device.
+ * Returns TTB_OK, TTB_ETIMEOUT, or another negative status. */
+TTB_API int ttb_check_device(int device_id);
+/* 1 if this view can be fed to the tensor-core kernels through a TMA
+ * descriptor (16-byte aligned base, unit stride on one matrix dim, other
+ * byte strides multiples of 16), else 0; `operand` 0 = lhs, 1 = rhs.
+ * Host-only, touches no device. */
+TTB_API int ttb_view_tma_eligible(const ttb_view *v, int dtype, int operand);
+TTB_API int ttb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TTB_H_ */

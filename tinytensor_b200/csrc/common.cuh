@@ -1,0 +1,67 @@
+// common.cuh -- types shared by the C ABI layer and the kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ttb.h"
+
+namespace ttb {
+
+// One batched product, fully resolved: element pointers already include the
+// view offsets, strides are in elements.
+// lhs[b,i,k] = a[b*a_sb + i*a_si + k*a_sk]
+// rhs[b,k,j] = b[b*b_sb + k*b_sk + j*b_sj]
+// out[b,i,j] = c[b*c_sb + i*c_si + j*c_sj]
+struct Problem {
+    const void *a;
+    const void *b;
+    void *c;
+    int64_t B, N, K, M;
+    int64_t a_sb, a_si, a_sk;
+    int64_t b_sb, b_sk, b_sj;
+    int64_t c_sb, c_si, c_sj;
+    int dtype;
+    int device;
+    cudaStream_t stream;
+};
+
+// Error word written by kernels whose bounded waits gave up.  One per device,
+// in ordinary global memory owned by the library.
+struct DeviceStatus {
+    unsigned int error;     // 0 = fine; otherwise a code naming the wait that gave up
+    unsigned int detail;    // stage / tile that was being waited for
+};
+
+enum DeviceErrorCode : unsigned int {
+    kErrNone = 0,
+    kErrProducerWait = 1,
+    kErrConverterWait = 2,
+    kErrMmaWait = 3,
+    kErrEpilogueWait = 4,
+    kErrAccEmptyWait = 5
+};
+
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+void note_launch(int variant, int count);
+
+// Returns the device-resident status word of `device` (allocated on first use).
+int device_status_ptr(int device, DeviceStatus **out);
+int sm_count(int device, int *out);
+
+// Per-dtype launchers.  Each returns a ttb_status.
+int launch_simt(const Problem &p, bool allow_splitk);
+struct F32Options {
+    int terms = 3;      // 3 = split-TF32; 1 = one TF32 pass (test only)
+    int k_chunk = 0;    // K blocks accumulated in TMEM before folding into registers (0 = all)
+    int two_cta = 0;    // use CTA pairs (cta_group::2)
+    int mask_big = 0;   // converters also rewrite the raw tile with its masked big part (test only)
+};
+int launch_f32_tcgen05(const Problem &p, const F32Options &opt);
+bool f32_tcgen05_eligible(const Problem &p, char *why, int why_len);
+int launch_f64_dmma(const Problem &p);
+bool f64_dmma_eligible(const Problem &p);
+
+size_t dtype_size(int dtype);
+
+}  // namespace ttb

@@ -1,0 +1,485 @@
+// gemm_f32_tcgen05.cu -- f32 batched GEMM on the 5th-generation tensor cores of sm_100a.
+//
+// C[b] = A[b] . B[b] in fp32-class accuracy from three TF32 tensor-core products
+// ("3xTF32"): every fp32 operand x is split as x = big + small with
+// big = x with its low 13 mantissa bits cleared (what kind::tf32 reads from an fp32
+// word) and small = x - big (exact in fp32).  Then
+//     A.B ~= big_A.big_B + small_A.big_B + big_A.small_B
+// and the dropped small.small term is below 2^-20 relative.
+//
+// Replaces matmul_kernel<float> of the reference
+// (tinytensor/tensor/backend/cuda/kernel/matmul.cuh:27-151), a 64x64x8 CUDA-core
+// kernel that needs contiguous operands.
+//
+// Structure of one CTA (persistent, one per SM, static round-robin over tiles):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the raw fp32 A and B
+//               tiles, through tensor maps built from the operand's own strides
+//               (K-major or MN-major, so transposed views need no copy);
+//   warps 6-9   converters: read the raw tile from shared memory, write the
+//               `small` tile (same offsets, so the swizzled layout is preserved),
+//               fence.proxy.async, signal;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma kind::tf32, three per
+//               K step, accumulating in TMEM; tcgen05.commit releases the stage;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, store C.  Two TMEM
+//               accumulators, so the epilogue of tile i overlaps the mainloop of
+//               tile i+1.
+// All waits are bounded: a wait that gives up writes an error word and the CTA
+// unwinds (TMEM freed) instead of hanging.
+#include <cuda.h>
+
+#include <cstdio>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tma_desc.cuh"
+
+namespace ttb {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;              // lhs rows per CTA
+constexpr int BNC = 128;             // rhs columns loaded per CTA
+constexpr int BK = 32;               // fp32 per K block = 128 bytes = one swizzle row
+constexpr int UMMA_K = 8;            // K of one tcgen05.mma kind::tf32
+constexpr int STAGES = 3;
+constexpr int TILE_BYTES = BM * BK * 4;        // 16 KiB: one operand tile
+constexpr int RAW_BYTES = 2 * TILE_BYTES;      // raw A + raw B
+constexpr int STAGE_BYTES = 2 * RAW_BYTES;     // + small A + small B
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
+constexpr int MN_BOX_BYTES = 32 * BK * 4;      // one MN-major TMA box: 32 (MN) x BK (K)
+
+constexpr int NUM_EPI_WARPS = 4;
+constexpr int NUM_CONV_WARPS = 4;
+constexpr int NUM_WARPS = 2 + NUM_EPI_WARPS + NUM_CONV_WARPS;
+constexpr int NUM_THREADS = NUM_WARPS * 32;
+constexpr int FIRST_EPI_WARP = 2;
+constexpr int FIRST_CONV_WARP = 2 + NUM_EPI_WARPS;
+
+struct alignas(64) TcArgs {
+    CUtensorMap tmap_a;
+    CUtensorMap tmap_b;
+    float *c;
+    long long c_sb, c_si, c_sj;
+    int N, M, K, B;
+    int a_mn_major, b_mn_major;
+    int a_batch_mul, b_batch_mul;
+    int tiles_m, tiles_n, total_tiles;
+    int terms;     // 3 = split-TF32, 1 = single pass (test only)
+    int mask_big;  // converters also overwrite the raw tile with its masked big part
+    DeviceStatus *status;
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait that also leaves early when another role of this CTA gave up.
+// Time limit: 2 s of %globaltimer.
+template <bool CLUSTER>
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        const bool ok = CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
+        if (ok) return true;
+        if ((i & 63u) == 63u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > 2000000000ull) return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void report(DeviceStatus *st, volatile int *abort_flag, unsigned code, unsigned detail) {
+    if (atomicCAS(&st->error, 0u, code) == 0u) st->detail = detail;
+    *abort_flag = 1;
+    __threadfence_block();
+}
+
+// Tile order: groups of 8 row tiles sweep all column tiles, so the CTAs running
+// at one time share A rows and B columns in L2.
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &b, int &tm, int &tn) {
+    const int per_batch = tiles_m * tiles_n;
+    b = t / per_batch;
+    const int r = t - b * per_batch;
+    constexpr int G = 8;
+    const int group_span = G * tiles_n;
+    const int g = r / group_span;
+    const int first_m = g * G;
+    const int gsz = (tiles_m - first_m) < G ? (tiles_m - first_m) : G;
+    const int in_g = r - g * group_span;
+    tm = first_m + in_g % gsz;
+    tn = in_g / gsz;
+}
+
+template <int CG>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const __grid_constant__ TcArgs args) {
+    static_assert(CG == 1, "only the single-CTA form is built here");
+    constexpr int UMMA_N = BNC * CG;
+    constexpr int ACC_COLS = UMMA_N;          // fp32 columns of one accumulator
+    constexpr int TMEM_COLS = 2 * ACC_COLS;   // two accumulators
+
+    extern __shared__ uint8_t smem_dyn[];
+    __shared__ uint64_t full_bar[STAGES];   // TMA bytes landed
+    __shared__ uint64_t conv_bar[STAGES];   // small tiles written
+    __shared__ uint64_t empty_bar[STAGES];  // MMAs that read the stage are done
+    __shared__ uint64_t acc_full_bar[2];
+    __shared__ uint64_t acc_empty_bar[2];
+    __shared__ uint64_t drain_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag_s;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    volatile int *abort_flag = &abort_flag_s;
+
+    // 1024-byte alignment of the tile area in the shared window (needed by the
+    // 128-byte swizzle: the XOR pattern repeats every 8 rows of 128 bytes).
+    const uint32_t dyn_base = smem_u32(smem_dyn);
+    const uint32_t tiles_base = (dyn_base + 1023u) & ~1023u;
+    uint8_t *tiles = smem_dyn + (tiles_base - dyn_base);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&conv_bar[s], NUM_CONV_WARPS);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full_bar[a], 1);
+            mbar_init(&acc_empty_bar[a], NUM_EPI_WARPS);
+        }
+        mbar_init(&drain_bar, 1);
+        abort_flag_s = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&args.tmap_a);
+        tma_prefetch_desc(&args.tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc<CG>(&tmem_base_slot, TMEM_COLS);
+        tmem_relinquish<CG>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int num_kb = (args.K + BK - 1) / BK;
+    const int first_tile = blockIdx.x;
+    const int tile_step = gridDim.x;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int issued = 0;
+            for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
+                int b, tm, tn;
+                tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
+                const int m0 = tm * BM, n0 = tn * BNC;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!wait_or_abort<false>(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                        report(args.status, abort_flag, kErrProducerWait, static_cast<unsigned>(stage));
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *a_dst = tiles + stage * STAGE_BYTES;
+                    uint8_t *b_dst = a_dst + TILE_BYTES;
+                    mbar_arrive_expect_tx(&full_bar[stage], RAW_BYTES);
+                    const int k0 = kb * BK;
+                    if (args.a_mn_major) {
+                        for (int j = 0; j < BM / 32; ++j)
+                            tma_load_3d(a_dst + j * MN_BOX_BYTES, &args.tmap_a, &full_bar[stage], m0 + 32 * j, k0,
+                                        b * args.a_batch_mul);
+                    } else {
+                        tma_load_3d(a_dst, &args.tmap_a, &full_bar[stage], k0, m0, b * args.a_batch_mul);
+                    }
+                    if (args.b_mn_major) {
+                        for (int j = 0; j < BNC / 32; ++j)
+                            tma_load_3d(b_dst + j * MN_BOX_BYTES, &args.tmap_b, &full_bar[stage], n0 + 32 * j, k0,
+                                        b * args.b_batch_mul);
+                    } else {
+                        tma_load_3d(b_dst, &args.tmap_b, &full_bar[stage], k0, n0, b * args.b_batch_mul);
+                    }
+                    ++issued;
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok && issued > 0) {
+                // Let the copies already in flight land before the CTA's shared
+                // memory is given up: wait (bounded) for the last stage issued.
+                const int last = (stage + STAGES - 1) % STAGES;
+                const uint32_t last_phase = (stage == 0) ? (phase ^ 1u) : phase;
+                for (int i = 0; i < 100000; ++i)
+                    if (mbar_try_wait(&full_bar[last], last_phase)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_tf32(BM * CG, UMMA_N, args.a_mn_major, args.b_mn_major);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            // Descriptor fields per operand major.
+            //  K-major : rows of 128 B, 8-row groups 1024 B apart (SBO); a K step of 8
+            //            fp32 advances the start address by 32 B inside the swizzle row.
+            //  MN-major: 32-element (128 B) MN groups MN_BOX_BYTES apart (LBO), 8-row K
+            //            groups 1024 B apart (SBO); a K step advances by 1024 B.
+            const uint32_t a_lbo = args.a_mn_major ? MN_BOX_BYTES : 16, a_kstep = args.a_mn_major ? 1024 : 32;
+            const uint32_t b_lbo = args.b_mn_major ? MN_BOX_BYTES : 16, b_kstep = args.b_mn_major ? 1024 : 32;
+            for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
+                if (!wait_or_abort<false>(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
+                    report(args.status, abort_flag, kErrAccEmptyWait, static_cast<unsigned>(acc));
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_COLS);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!wait_or_abort<false>(&conv_bar[stage], phase, abort_flag) ||
+                        !wait_or_abort<false>(&full_bar[stage], phase, abort_flag)) {
+                        report(args.status, abort_flag, kErrMmaWait, static_cast<unsigned>(stage));
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_raw = tiles_base + stage * STAGE_BYTES;
+                    const uint32_t b_raw = a_raw + TILE_BYTES;
+                    const uint32_t a_small = a_raw + RAW_BYTES;
+                    const uint32_t b_small = b_raw + RAW_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t da_big = make_smem_desc(a_raw + kk * a_kstep, a_lbo, 1024, kSwizzle128);
+                        const uint64_t db_big = make_smem_desc(b_raw + kk * b_kstep, b_lbo, 1024, kSwizzle128);
+                        if (args.terms == 3) {
+                            const uint64_t da_small =
+                                make_smem_desc(a_small + kk * a_kstep, a_lbo, 1024, kSwizzle128);
+                            const uint64_t db_small =
+                                make_smem_desc(b_small + kk * b_kstep, b_lbo, 1024, kSwizzle128);
+                            // Small terms first: they are ~2^-11 of the big term.
+                            mma_tf32<CG>(d_tmem, da_small, db_big, idesc, (kb | kk) != 0);
+                            mma_tf32<CG>(d_tmem, da_big, db_small, idesc, 1);
+                            mma_tf32<CG>(d_tmem, da_big, db_big, idesc, 1);
+                        } else {
+                            mma_tf32<CG>(d_tmem, da_big, db_big, idesc, (kb | kk) != 0);
+                        }
+                    }
+                    mma_commit<CG>(smem_u32(&empty_bar[stage]));
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                mma_commit<CG>(smem_u32(&acc_full_bar[acc]));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+            // Everything issued must have retired before TMEM is freed.
+            mma_commit<CG>(smem_u32(&drain_bar));
+            for (int i = 0; i < 1000000; ++i)
+                if (mbar_try_wait(&drain_bar, 0)) break;
+        }
+    } else if (warp < FIRST_CONV_WARP) {
+        // ------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, +32)
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        const bool vec_ok = args.c_sj == 1 && (args.c_si & 3) == 0 && (args.c_sb & 3) == 0 &&
+                            (reinterpret_cast<uintptr_t>(args.c) & 15) == 0;
+        for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
+            int b, tm, tn;
+            tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
+            if (!wait_or_abort<false>(&acc_full_bar[acc], acc_phase, abort_flag)) {
+                if (lane == 0) report(args.status, abort_flag, kErrEpilogueWait, static_cast<unsigned>(acc));
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const int row = tm * BM + quarter * 32 + lane;
+            const int n0 = tn * BNC;
+            float *crow = args.c + static_cast<long long>(b) * args.c_sb + static_cast<long long>(row) * args.c_si;
+            const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * ACC_COLS) +
+                                   (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int ch = 0; ch < BNC / 32; ++ch) {
+                const int col0 = n0 + ch * 32;
+                if (col0 >= args.M) break;  // warp-uniform
+                uint32_t v[32];
+                tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
+                tmem_ld_wait();
+                if (row < args.N) {
+                    if (vec_ok && col0 + 32 <= args.M) {
+                        float4 *dst = reinterpret_cast<float4 *>(crow + col0);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            dst[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                 __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < args.M)
+                                crow[static_cast<long long>(col0 + j) * args.c_sj] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    } else {
+        // ------------------------------------------------------------ converters
+        const int ctid = threadIdx.x - FIRST_CONV_WARP * 32;
+        constexpr int NCT = NUM_CONV_WARPS * 32;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const bool mask_big = args.mask_big != 0;
+        for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!wait_or_abort<false>(&full_bar[stage], phase, abort_flag)) {
+                    if (lane == 0) report(args.status, abort_flag, kErrConverterWait, static_cast<unsigned>(stage));
+                    ok = false;
+                    break;
+                }
+                uint4 *raw = reinterpret_cast<uint4 *>(tiles + stage * STAGE_BYTES);
+                uint4 *small = reinterpret_cast<uint4 *>(tiles + stage * STAGE_BYTES + RAW_BYTES);
+#pragma unroll 4
+                for (int i = ctid; i < RAW_BYTES / 16; i += NCT) {
+                    const uint4 x = raw[i];
+                    uint4 big, sm;
+                    big.x = x.x & 0xFFFFE000u;
+                    big.y = x.y & 0xFFFFE000u;
+                    big.z = x.z & 0xFFFFE000u;
+                    big.w = x.w & 0xFFFFE000u;
+                    sm.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(big.x));
+                    sm.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(big.y));
+                    sm.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(big.z));
+                    sm.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(big.w));
+                    small[i] = sm;
+                    if (mask_big) raw[i] = big;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&conv_bar[stage]);
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc<CG>(tmem_base, TMEM_COLS);
+    }
+}
+
+struct TcPlan {
+    OperandView a, b;
+    OperandMajor a_major, b_major;
+};
+
+bool plan(const Problem &p, TcPlan *pl, char *why, int why_len) {
+    if (p.N > 0x7FFFFFFFLL || p.M > 0x7FFFFFFFLL || p.K > 0x7FFFFFFFLL || p.B > 0x7FFFFFFFLL) {
+        if (why) snprintf(why, why_len, "extent above 2^31-1");
+        return false;
+    }
+    pl->a = OperandView{p.a, p.N, p.K, p.B, p.a_si, p.a_sk, p.a_sb};
+    pl->b = OperandView{p.b, p.M, p.K, p.B, p.b_sj, p.b_sk, p.b_sb};
+    char w[128] = "";
+    pl->a_major = classify_operand(pl->a, 4, w, sizeof(w));
+    if (pl->a_major == kMajorNone) {
+        if (why) snprintf(why, why_len, "lhs: %s", w);
+        return false;
+    }
+    pl->b_major = classify_operand(pl->b, 4, w, sizeof(w));
+    if (pl->b_major == kMajorNone) {
+        if (why) snprintf(why, why_len, "rhs: %s", w);
+        return false;
+    }
+    const long long tiles = ((p.N + BM - 1) / BM) * ((p.M + BNC - 1) / BNC) * p.B;
+    if (tiles > 0x7FFFFFFFLL) {
+        if (why) snprintf(why, why_len, "too many tiles");
+        return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+bool f32_tcgen05_eligible(const Problem &p, char *why, int why_len) {
+    TcPlan pl;
+    return plan(p, &pl, why, why_len);
+}
+
+int launch_f32_tcgen05(const Problem &p, const F32Options &opt) {
+    TcPlan pl;
+    char why[200] = "";
+    if (!plan(p, &pl, why, sizeof(why))) {
+        set_error("tcgen05 f32 kernel cannot take these views: %s", why);
+        return TTB_EUNSUPPORTED;
+    }
+    TcArgs args;
+    memset(&args, 0, sizeof(args));
+    if (encode_operand_tmap(&args.tmap_a, pl.a, pl.a_major, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, 32, BM, BK,
+                            &args.a_batch_mul, why, sizeof(why)) ||
+        encode_operand_tmap(&args.tmap_b, pl.b, pl.b_major, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, 32, BNC, BK,
+                            &args.b_batch_mul, why, sizeof(why))) {
+        set_error("tensor map: %s", why);
+        return TTB_EUNSUPPORTED;
+    }
+    args.c = static_cast<float *>(p.c);
+    args.c_sb = p.c_sb;
+    args.c_si = p.c_si;
+    args.c_sj = p.c_sj;
+    args.N = static_cast<int>(p.N);
+    args.M = static_cast<int>(p.M);
+    args.K = static_cast<int>(p.K);
+    args.B = static_cast<int>(p.B);
+    args.a_mn_major = pl.a_major == kMajorMN;
+    args.b_mn_major = pl.b_major == kMajorMN;
+    args.tiles_m = static_cast<int>((p.N + BM - 1) / BM);
+    args.tiles_n = static_cast<int>((p.M + BNC - 1) / BNC);
+    args.total_tiles = args.tiles_m * args.tiles_n * args.B;
+    args.terms = opt.terms;
+    args.mask_big = opt.mask_big;
+    int rc = device_status_ptr(p.device, &args.status);
+    if (rc != TTB_OK) return rc;
+    int sms = 148;
+    sm_count(p.device, &sms);
+    static bool attr_set[64] = {false};
+    if (!attr_set[p.device & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_f32_3xtf32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SMEM_BYTES);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
+        attr_set[p.device & 63] = true;
+    }
+    const int grid = args.total_tiles < sms ? args.total_tiles : sms;
+    gemm_f32_3xtf32_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, p.stream>>>(args);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_f32_3xtf32_kernel launch");
+    note_launch(TTB_VARIANT_TCGEN05_3XTF32, 1);
+    return TTB_OK;
+}
+
+}  // namespace ttb

@@ -1,0 +1,534 @@
+// ttb_api.cu -- the extern "C" layer: argument checking, view resolution,
+// kernel dispatch, per-device workspaces and the host-buffer entry point.
+//
+// Mirrors the contract of tinytensor::cuda::batched_matmul_runner
+// (tinytensor/tensor/backend/cuda/matmul.cu:26-78): rank-3 operands of one dtype
+// on one device, result contiguous [B,N,M].  Differences, all deliberate:
+//  * strided views are consumed as they are (the reference clones them first,
+//    matmul.cu:40-41);
+//  * lhs.size(0) == rhs.size(0) is checked (the reference reads B from lhs only,
+//    matmul.cu:30);
+//  * errors come back as status codes instead of assert/exit.
+// There is no CPU fallback anywhere in this library.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ttb {
+
+namespace {
+thread_local char g_err[512] = "";
+thread_local int g_last_variant = 0;
+thread_local long long g_launches = 0;
+
+struct Options {
+    int force_variant = TTB_VARIANT_AUTO;
+    int tf32_terms = 3;
+    int k_chunk = 0;
+    int splitk = 1;
+    int two_cta = 0;
+    int mask_big = 0;
+};
+Options g_opt;
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    bool init = false;
+    int sms = 0;
+    DeviceStatus *status = nullptr;
+    void *workspace = nullptr;
+    size_t workspace_bytes = 0;
+    void *stage[3] = {nullptr, nullptr, nullptr};
+    size_t stage_bytes[3] = {0, 0, 0};
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+}  // namespace
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+    set_error("%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+    return e == cudaErrorMemoryAllocation ? TTB_ENOMEM : TTB_ECUDA;
+}
+
+void note_launch(int variant, int count) {
+    g_last_variant = variant;
+    g_launches += count;
+}
+
+size_t dtype_size(int dtype) {
+    switch (dtype) {
+        case TTB_U8: return 1;
+        case TTB_I16: return 2;
+        case TTB_I32: return 4;
+        case TTB_I64: return 8;
+        case TTB_F32: return 4;
+        case TTB_F64: return 8;
+        default: return 0;
+    }
+}
+
+static int device_state(int device, DeviceState **out) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceCount");
+    if (device < 0 || device >= n || device >= kMaxDevices) {
+        set_error("device id %d out of range (have %d)", device, n);
+        return TTB_EDEVICE;
+    }
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState &d = g_dev[device];
+    if (!d.init) {
+        e = cudaSetDevice(device);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+        e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+        e = cudaMalloc(&d.status, sizeof(DeviceStatus));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(status)");
+        e = cudaMemset(d.status, 0, sizeof(DeviceStatus));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(status)");
+        d.init = true;
+    }
+    *out = &d;
+    return TTB_OK;
+}
+
+int device_status_ptr(int device, DeviceStatus **out) {
+    DeviceState *d;
+    int rc = device_state(device, &d);
+    if (rc != TTB_OK) return rc;
+    *out = d->status;
+    return TTB_OK;
+}
+
+int sm_count(int device, int *out) {
+    DeviceState *d;
+    int rc = device_state(device, &d);
+    if (rc != TTB_OK) return rc;
+    *out = d->sms;
+    return TTB_OK;
+}
+
+// Scratch for split-K partials: cached per device, grown on demand.  Growing
+// frees the old buffer, which synchronises the device, so earlier kernels that
+// used it have finished.
+int workspace_get(int device, size_t bytes, void **out) {
+    DeviceState *d;
+    int rc = device_state(device, &d);
+    if (rc != TTB_OK) return rc;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (d->workspace_bytes < bytes) {
+        if (d->workspace) cudaFree(d->workspace);
+        d->workspace = nullptr;
+        d->workspace_bytes = 0;
+        size_t want = bytes + (bytes >> 2);
+        cudaError_t e = cudaMalloc(&d->workspace, want);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(workspace)");
+        d->workspace_bytes = want;
+    }
+    *out = d->workspace;
+    return TTB_OK;
+}
+
+static int stage_get(DeviceState *d, int which, size_t bytes, void **out) {
+    if (d->stage_bytes[which] < bytes) {
+        if (d->stage[which]) cudaFree(d->stage[which]);
+        d->stage[which] = nullptr;
+        d->stage_bytes[which] = 0;
+        cudaError_t e = cudaMalloc(&d->stage[which], bytes);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(staging)");
+        d->stage_bytes[which] = bytes;
+    }
+    *out = d->stage[which];
+    return TTB_OK;
+}
+
+// Number of elements the view spans in its storage, from its first element.
+static int64_t view_span(const ttb_view *v) {
+    int64_t last = 0;
+    for (int i = 0; i < 3; ++i) last += (v->size[i] - 1) * v->stride[i];
+    return last + 1;
+}
+
+static int check_view(const ttb_view *v, const char *name) {
+    if (!v || !v->data) {
+        set_error("%s: null view or data pointer", name);
+        return TTB_EINVAL;
+    }
+    if (v->offset < 0) {
+        set_error("%s: negative offset %lld", name, static_cast<long long>(v->offset));
+        return TTB_EINVAL;
+    }
+    for (int i = 0; i < 3; ++i) {
+        if (v->size[i] < 1) {
+            set_error("%s: size[%d] = %lld, must be >= 1", name, i, static_cast<long long>(v->size[i]));
+            return TTB_ESHAPE;
+        }
+        if (v->stride[i] < 0) {
+            set_error("%s: negative stride[%d] = %lld", name, i, static_cast<long long>(v->stride[i]));
+            return TTB_EINVAL;
+        }
+        if (v->size[i] > (1LL << 31) - 1) {
+            set_error("%s: size[%d] = %lld exceeds 2^31-1", name, i, static_cast<long long>(v->size[i]));
+            return TTB_ESHAPE;
+        }
+    }
+    return TTB_OK;
+}
+
+static int resolve(const ttb_view *lhs, const ttb_view *rhs, void *out, int64_t out_offset,
+                   const int64_t out_stride[3], int dtype, int device, void *stream, Problem *p) {
+    const size_t es = dtype_size(dtype);
+    if (dtype == TTB_BOOL8) {
+        set_error("matmul is not defined for bool8");
+        return TTB_EDTYPE;
+    }
+    if (es == 0) {
+        set_error("unknown dtype %d", dtype);
+        return TTB_EDTYPE;
+    }
+    int rc = check_view(lhs, "lhs");
+    if (rc != TTB_OK) return rc;
+    rc = check_view(rhs, "rhs");
+    if (rc != TTB_OK) return rc;
+    if (!out) {
+        set_error("out: null pointer");
+        return TTB_EINVAL;
+    }
+    if (lhs->size[0] != rhs->size[0]) {
+        set_error("batch sizes differ: lhs %lld vs rhs %lld", static_cast<long long>(lhs->size[0]),
+                  static_cast<long long>(rhs->size[0]));
+        return TTB_ESHAPE;
+    }
+    if (lhs->size[2] != rhs->size[1]) {
+        set_error("inner dims differ: lhs[.,.,%lld] vs rhs[.,%lld,.]", static_cast<long long>(lhs->size[2]),
+                  static_cast<long long>(rhs->size[1]));
+        return TTB_ESHAPE;
+    }
+    p->B = lhs->size[0];
+    p->N = lhs->size[1];
+    p->K = lhs->size[2];
+    p->M = rhs->size[2];
+    // The reference holds element counts in `int` (tinytensor/tensor/shape.cpp:33).
+    const long double out_elems = static_cast<long double>(p->B) * p->N * p->M;
+    if (out_elems > 9.0e18L) {
+        set_error("result too large");
+        return TTB_ESHAPE;
+    }
+    p->a = static_cast<const char *>(lhs->data) + lhs->offset * es;
+    p->b = static_cast<const char *>(rhs->data) + rhs->offset * es;
+    p->a_sb = lhs->stride[0];
+    p->a_si = lhs->stride[1];
+    p->a_sk = lhs->stride[2];
+    p->b_sb = rhs->stride[0];
+    p->b_sk = rhs->stride[1];
+    p->b_sj = rhs->stride[2];
+    if (out_stride) {
+        if (out_offset < 0 || out_stride[0] < 0 || out_stride[1] < 0 || out_stride[2] < 0) {
+            set_error("out: negative offset or stride");
+            return TTB_EINVAL;
+        }
+        p->c = static_cast<char *>(out) + out_offset * es;
+        p->c_sb = out_stride[0];
+        p->c_si = out_stride[1];
+        p->c_sj = out_stride[2];
+    } else {
+        p->c = out;
+        p->c_sb = p->N * p->M;
+        p->c_si = p->M;
+        p->c_sj = 1;
+    }
+    p->dtype = dtype;
+    p->device = device;
+    p->stream = static_cast<cudaStream_t>(stream);
+    return TTB_OK;
+}
+
+static F32Options f32_options(bool two_cta) {
+    F32Options o;
+    o.terms = g_opt.tf32_terms;
+    o.k_chunk = g_opt.k_chunk;
+    o.two_cta = two_cta ? 1 : 0;
+    o.mask_big = g_opt.mask_big;
+    return o;
+}
+
+static int dispatch(const Problem &p) {
+    DeviceState *d;
+    int rc = device_state(p.device, &d);
+    if (rc != TTB_OK) return rc;
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (cur != p.device) {
+        // The reference selects the device before every launch (kernel_launch.cuh:20).
+        cudaError_t e = cudaSetDevice(p.device);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    }
+    const int force = g_opt.force_variant;
+    char why[160] = "";
+    switch (force) {
+        case TTB_VARIANT_SIMT: return launch_simt(p, false);
+        case TTB_VARIANT_SIMT_SPLITK: return launch_simt(p, true);
+        case TTB_VARIANT_TCGEN05_3XTF32:
+        case TTB_VARIANT_TCGEN05_2CTA:
+            if (p.dtype != TTB_F32 || !f32_tcgen05_eligible(p, why, sizeof(why))) {
+                set_error("forced tcgen05 variant cannot take this call: %s",
+                          p.dtype != TTB_F32 ? "dtype is not f32" : why);
+                return TTB_EUNSUPPORTED;
+            }
+            return launch_f32_tcgen05(p, f32_options(force == TTB_VARIANT_TCGEN05_2CTA));
+        case TTB_VARIANT_DMMA_F64:
+            if (p.dtype != TTB_F64 || !f64_dmma_eligible(p)) {
+                set_error("forced DMMA variant cannot take this call");
+                return TTB_EUNSUPPORTED;
+            }
+            return launch_f64_dmma(p);
+        default: break;
+    }
+    // Automatic dispatch.
+    if (p.dtype == TTB_F32) {
+        // Tensor cores pay off once the product has enough work per output tile;
+        // skinny outputs (a dim <= 16) are bandwidth-bound and go to the SIMT kernel.
+        const bool big = p.N > 16 && p.M > 16 && p.K >= 16 &&
+                         static_cast<double>(p.N) * p.M * p.K * p.B >= 128.0 * 128.0 * 64.0;
+        if (big && f32_tcgen05_eligible(p, why, sizeof(why)))
+            return launch_f32_tcgen05(p, f32_options(g_opt.two_cta != 0));
+        return launch_simt(p, g_opt.splitk != 0);
+    }
+    if (p.dtype == TTB_F64) {
+        if (p.N > 16 && p.M > 16 && f64_dmma_eligible(p)) return launch_f64_dmma(p);
+        return launch_simt(p, g_opt.splitk != 0);
+    }
+    return launch_simt(p, g_opt.splitk != 0);
+}
+
+}  // namespace ttb
+
+using namespace ttb;
+
+extern "C" {
+
+TTB_API int ttb_batched_matmul(const ttb_view *lhs, const ttb_view *rhs, void *out, int dtype, int device_id,
+                               void *stream) {
+    Problem p{};
+    int rc = resolve(lhs, rhs, out, 0, nullptr, dtype, device_id, stream, &p);
+    if (rc != TTB_OK) return rc;
+    return dispatch(p);
+}
+
+TTB_API int ttb_batched_matmul_strided_out(const ttb_view *lhs, const ttb_view *rhs, void *out,
+                                           int64_t out_offset, const int64_t out_stride[3], int dtype,
+                                           int device_id, void *stream) {
+    if (!out_stride) {
+        set_error("out_stride: null pointer");
+        return TTB_EINVAL;
+    }
+    Problem p{};
+    int rc = resolve(lhs, rhs, out, out_offset, out_stride, dtype, device_id, stream, &p);
+    if (rc != TTB_OK) return rc;
+    return dispatch(p);
+}
+
+TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, void *out, int dtype,
+                                    int device_id) {
+    Problem p{};
+    int rc = resolve(lhs, rhs, out, 0, nullptr, dtype, device_id, nullptr, &p);
+    if (rc != TTB_OK) return rc;
+    DeviceState *d;
+    rc = device_state(device_id, &d);
+    if (rc != TTB_OK) return rc;
+    cudaError_t e = cudaSetDevice(device_id);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    const size_t es = dtype_size(dtype);
+    const size_t a_bytes = static_cast<size_t>(view_span(lhs)) * es;
+    const size_t b_bytes = static_cast<size_t>(view_span(rhs)) * es;
+    const size_t c_bytes = static_cast<size_t>(p.B) * p.N * p.M * es;
+    void *da, *db, *dc;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if ((rc = stage_get(d, 0, a_bytes, &da)) != TTB_OK) return rc;
+        if ((rc = stage_get(d, 1, b_bytes, &db)) != TTB_OK) return rc;
+        if ((rc = stage_get(d, 2, c_bytes, &dc)) != TTB_OK) return rc;
+    }
+    // Only the span each view touches travels; strides are kept, so the device
+    // side consumes the same (possibly permuted) view.
+    e = cudaMemcpyAsync(da, p.a, a_bytes, cudaMemcpyHostToDevice, nullptr);
+    if (e != cudaSuccess) return cuda_fail(e, "H2D lhs");
+    e = cudaMemcpyAsync(db, p.b, b_bytes, cudaMemcpyHostToDevice, nullptr);
+    if (e != cudaSuccess) return cuda_fail(e, "H2D rhs");
+    p.a = da;
+    p.b = db;
+    p.c = dc;
+    rc = dispatch(p);
+    if (rc != TTB_OK) return rc;
+    e = cudaMemcpyAsync(out, dc, c_bytes, cudaMemcpyDeviceToHost, nullptr);
+    if (e != cudaSuccess) return cuda_fail(e, "D2H out");
+    e = cudaStreamSynchronize(nullptr);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    return TTB_OK;
+}
+
+TTB_API int ttb_partition(int64_t B, int64_t N, int64_t K, int64_t M, int world, int rank, int64_t col_align,
+                          int64_t *begin, int64_t *end) {
+    if (!begin || !end || world < 1 || rank < 0 || rank >= world) {
+        set_error("ttb_partition: bad world/rank or null output");
+        return TTB_EINVAL;
+    }
+    if (B < 1 || N < 1 || K < 1 || M < 1) {
+        set_error("ttb_partition: sizes must be >= 1");
+        return TTB_ESHAPE;
+    }
+    if (col_align < 1) col_align = 1;
+    if (B > 1) {
+        // Contiguous batch ranges, sizes differing by at most one.
+        const int64_t base = B / world, rem = B % world;
+        const int64_t b0 = rank * base + (rank < rem ? rank : rem);
+        *begin = b0;
+        *end = b0 + base + (rank < rem ? 1 : 0);
+        return 0;
+    }
+    // Column blocks in units of col_align columns.
+    const int64_t units = (M + col_align - 1) / col_align;
+    const int64_t base = units / world, rem = units % world;
+    const int64_t u0 = rank * base + (rank < rem ? rank : rem);
+    const int64_t u1 = u0 + base + (rank < rem ? 1 : 0);
+    int64_t c0 = u0 * col_align, c1 = u1 * col_align;
+    if (c0 > M) c0 = M;
+    if (c1 > M) c1 = M;
+    *begin = c0;
+    *end = c1;
+    return 1;
+}
+
+TTB_API const char *ttb_last_error(void) { return g_err; }
+TTB_API int ttb_last_variant(void) { return g_last_variant; }
+TTB_API int64_t ttb_launch_count(void) { return g_launches; }
+
+TTB_API const char *ttb_variant_name(int variant) {
+    switch (variant) {
+        case TTB_VARIANT_AUTO: return "auto";
+        case TTB_VARIANT_SIMT: return "simt";
+        case TTB_VARIANT_TCGEN05_3XTF32: return "tcgen05_3xtf32";
+        case TTB_VARIANT_DMMA_F64: return "dmma_f64";
+        case TTB_VARIANT_SIMT_SPLITK: return "simt_splitk";
+        case TTB_VARIANT_TCGEN05_2CTA: return "tcgen05_3xtf32_2cta";
+        default: return "unknown";
+    }
+}
+
+TTB_API int ttb_set_option(const char *key, int64_t value) {
+    if (!key) {
+        set_error("ttb_set_option: null key");
+        return TTB_EINVAL;
+    }
+    if (!strcmp(key, "force_variant")) {
+        if (value < 0 || value > TTB_VARIANT_TCGEN05_2CTA) {
+            set_error("force_variant: %lld is not a variant", static_cast<long long>(value));
+            return TTB_EINVAL;
+        }
+        g_opt.force_variant = static_cast<int>(value);
+        return TTB_OK;
+    }
+    if (!strcmp(key, "tf32_terms")) {
+        if (value != 1 && value != 3) {
+            set_error("tf32_terms must be 1 or 3");
+            return TTB_EINVAL;
+        }
+        g_opt.tf32_terms = static_cast<int>(value);
+        return TTB_OK;
+    }
+    if (!strcmp(key, "k_chunk")) {
+        if (value < 0 || value > (1 << 20)) {
+            set_error("k_chunk out of range");
+            return TTB_EINVAL;
+        }
+        g_opt.k_chunk = static_cast<int>(value);
+        return TTB_OK;
+    }
+    if (!strcmp(key, "splitk")) {
+        g_opt.splitk = value != 0;
+        return TTB_OK;
+    }
+    if (!strcmp(key, "two_cta")) {
+        g_opt.two_cta = value != 0;
+        return TTB_OK;
+    }
+    if (!strcmp(key, "mask_big")) {
+        g_opt.mask_big = value != 0;
+        return TTB_OK;
+    }
+    set_error("unknown option '%s'", key);
+    return TTB_EINVAL;
+}
+
+TTB_API int64_t ttb_get_option(const char *key) {
+    if (!key) return TTB_EINVAL;
+    if (!strcmp(key, "force_variant")) return g_opt.force_variant;
+    if (!strcmp(key, "tf32_terms")) return g_opt.tf32_terms;
+    if (!strcmp(key, "k_chunk")) return g_opt.k_chunk;
+    if (!strcmp(key, "splitk")) return g_opt.splitk;
+    if (!strcmp(key, "two_cta")) return g_opt.two_cta;
+    if (!strcmp(key, "mask_big")) return g_opt.mask_big;
+    set_error("unknown option '%s'", key);
+    return TTB_EINVAL;
+}
+
+TTB_API int ttb_device_count(void) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceCount");
+    return n;
+}
+
+TTB_API int ttb_check_device(int device_id) {
+    DeviceState *d;
+    int rc = device_state(device_id, &d);
+    if (rc != TTB_OK) return rc;
+    cudaError_t e = cudaSetDevice(device_id);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+    DeviceStatus h{};
+    e = cudaMemcpy(&h, d->status, sizeof(h), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
+    if (h.error != 0) {
+        cudaMemset(d->status, 0, sizeof(DeviceStatus));
+        set_error("device %d: a bounded wait inside a kernel gave up (code %u, detail %u)", device_id, h.error,
+                  h.detail);
+        return TTB_ETIMEOUT;
+    }
+    return TTB_OK;
+}
+
+TTB_API int ttb_view_tma_eligible(const ttb_view *v, int dtype, int operand) {
+    if (!v || (operand != 0 && operand != 1)) return 0;
+    const size_t es = dtype_size(dtype);
+    if (es == 0) return 0;
+    for (int i = 0; i < 3; ++i)
+        if (v->size[i] < 1 || v->stride[i] < 0) return 0;
+    // Matrix dims of the view: (rows, cols) = (size[1], size[2]).  For lhs the
+    // K dim is cols, for rhs it is rows; eligibility is symmetric in that.
+    const uintptr_t base = reinterpret_cast<uintptr_t>(v->data) + static_cast<uintptr_t>(v->offset) * es;
+    if (base % 16 != 0) return 0;
+    const int64_t s1 = v->stride[1], s2 = v->stride[2];
+    const int64_t n1 = v->size[1], n2 = v->size[2];
+    auto ok_outer = [&](int64_t stride, int64_t n) { return n == 1 || (stride > 0 && (stride * es) % 16 == 0); };
+    const bool inner2 = (s2 == 1 || n2 == 1) && ok_outer(s1, n1);
+    const bool inner1 = (s1 == 1 || n1 == 1) && ok_outer(s2, n2);
+    if (!inner1 && !inner2) return 0;
+    if (v->size[0] > 1 && v->stride[0] != 0 && (v->stride[0] * es) % 16 != 0) return 0;
+    return 1;
+}
+
+TTB_API int ttb_version(void) { return 100; }
+
+}  // extern "C"
