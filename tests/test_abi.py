@@ -1,0 +1,119 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol the header
+declares, and the host-only entry points behave.  No compute call is made here."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "ttb.h").read_text()
+    return sorted(set(re.findall(r"TTB_API\s+[\w\s\*]+?\b(ttb_\w+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    names = declared_symbols()
+    assert "ttb_batched_matmul" in names and "ttb_batched_matmul_host" in names
+    assert len(names) >= 12
+
+
+def test_library_exports_every_declared_symbol(ttb):
+    L = ttb.lib()
+    for name in declared_symbols():
+        assert hasattr(L, name), f"libttb.so does not export {name}"
+
+
+def test_version_and_variant_names(ttb):
+    L = ttb.lib()
+    assert L.ttb_version() >= 100
+    assert L.ttb_variant_name(1) == b"simt"
+    assert L.ttb_variant_name(2) == b"tcgen05_3xtf32"
+    assert L.ttb_variant_name(99) == b"unknown"
+
+
+def test_options_round_trip_and_reject_bad_values(ttb, reset_options):
+    ttb.set_option("force_variant", 1)
+    assert ttb.get_option("force_variant") == 1
+    with pytest.raises(ttb.TTBError):
+        ttb.set_option("force_variant", 77)
+    with pytest.raises(ttb.TTBError):
+        ttb.set_option("tf32_terms", 2)
+    with pytest.raises(ttb.TTBError):
+        ttb.set_option("no_such_option", 1)
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+def test_partition_batch_ranges_cover_exactly(ttb, world):
+    for B in (2, 7, 64, 256):
+        covered = []
+        for r in range(world):
+            p = ttb.partition(B, 128, 64, 128, world, r)
+            assert p.kind == "batch"
+            covered.extend(range(p.begin, p.end))
+        assert covered == list(range(B))
+        sizes = [ttb.partition(B, 128, 64, 128, world, r).size for r in range(world)]
+        assert max(sizes) - min(sizes) <= 1
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_partition_column_blocks_cover_exactly(ttb, world):
+    for M in (8192, 1000, 130, 64):
+        covered = []
+        for r in range(world):
+            p = ttb.partition(1, 4096, 512, M, world, r)
+            assert p.kind == "columns"
+            assert p.begin % 128 == 0 or p.begin == M
+            covered.extend(range(p.begin, p.end))
+        assert covered == list(range(M))
+    p = ttb.partition(1, 8192, 8192, 8192, 8, 3)
+    assert (p.begin, p.end) == (3072, 4096)
+
+
+def test_partition_rejects_bad_arguments(ttb):
+    with pytest.raises(ttb.TTBError):
+        ttb.partition(1, 8, 8, 8, 0, 0)
+    with pytest.raises(ttb.TTBError):
+        ttb.partition(1, 8, 8, 8, 2, 2)
+    with pytest.raises(ttb.TTBError):
+        ttb.partition(0, 8, 8, 8, 2, 0)
+
+
+def test_tma_eligibility_table(ttb):
+    """Host-only classification of views: which ones the tensor-core kernels can read
+    through a tensor map built from their strides."""
+    base = torch.zeros(4 * 64 * 96 + 8, dtype=torch.float32)
+    t = base[:4 * 64 * 96].view(4, 64, 96)
+    assert ttb.tma_eligible(t, 0)                       # contiguous
+    assert ttb.tma_eligible(t.permute(0, 2, 1), 1)      # transposed view (backward's operand)
+    assert ttb.tma_eligible(t[:, :, 32:64], 1)          # column block: strided, aligned
+    assert ttb.tma_eligible(t[1:2], 0)                  # offset batch
+    assert ttb.tma_eligible(t[:1].expand(4, 64, 96), 0)  # broadcast batch (stride 0)
+    assert not ttb.tma_eligible(t[:, :, ::2], 0)        # step on the inner dim
+    assert not ttb.tma_eligible(base[1:1 + 64 * 96].view(1, 64, 96), 0)  # 4-byte offset
+    assert not ttb.tma_eligible(t[:, :, :10].contiguous(), 0)  # 40-byte rows
+    assert not ttb.tma_eligible(t[:, :1, :].expand(4, 64, 96), 0)  # stride 0 on a matrix dim
+
+
+def test_compute_call_without_gpu_fails_loudly(ttb):
+    """No CPU fallback: on a box without CUDA the call reports an error."""
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    a = np.ones((1, 4, 4), dtype=np.float32)
+    with pytest.raises(ttb.TTBError):
+        ttb.batched_matmul_host(a, a)
+    with pytest.raises(ttb.TTBError):
+        ttb.batched_matmul(torch.ones(1, 4, 4), torch.ones(1, 4, 4))
+
+
+def test_missing_library_fails_loudly(ttb, monkeypatch, tmp_path):
+    from tinytensor_b200 import backend
+
+    monkeypatch.setenv("TTB_LIBRARY", str(tmp_path / "nope.so"))
+    monkeypatch.setattr(backend, "_lib", None)
+    with pytest.raises(ttb.TTBError):
+        backend.lib()

@@ -1,0 +1,150 @@
+"""Parity tests specific to the tcgen05 / TMEM / TMA f32 kernel (split-TF32).
+
+The kernel is forced, so a view it cannot take is an error rather than a silent detour
+through the SIMT kernel.  Operand layouts cover the four major combinations that forward
+and backward produce: row-major lhs (K-major), transposed-view lhs (MN-major), row-major
+rhs (MN-major) and transposed-view rhs (K-major)."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import dev, host, rel_to_max
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+
+
+@pytest.fixture()
+def forced(ttb, reset_options):
+    ttb.set_option("force_variant", int(ttb.Variant.TCGEN05_3XTF32))
+    return ttb
+
+
+def padded(t: torch.Tensor, pad_to: int = 4) -> torch.Tensor:
+    """Same values, but the innermost extent of the STORAGE is rounded up to `pad_to`
+    elements so that row strides are multiples of 16 bytes (a TMA requirement); the view
+    keeps the ragged logical shape, which exercises out-of-bounds zero fill."""
+    *lead, n = t.shape
+    npad = (n + pad_to - 1) // pad_to * pad_to
+    store = torch.zeros((*lead, npad), dtype=t.dtype, device=t.device)
+    store[..., :n] = t
+    return store[..., :n]
+
+
+def layouts(a: torch.Tensor, b: torch.Tensor):
+    """The four operand-major combinations of the same logical product."""
+    a_k = padded(a)                                             # [B,N,K] K contiguous
+    a_mn = padded(a.permute(0, 2, 1).contiguous()).permute(0, 2, 1)  # N contiguous
+    b_mn = padded(b)                                            # [B,K,M] M contiguous
+    b_k = padded(b.permute(0, 2, 1).contiguous()).permute(0, 2, 1)   # K contiguous
+    return {"kmaj.mnmaj": (a_k, b_mn), "kmaj.kmaj": (a_k, b_k), "mnmaj.mnmaj": (a_mn, b_mn),
+            "mnmaj.kmaj": (a_mn, b_k)}
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 32, 128), (1, 128, 64, 128), (2, 256, 96, 384), (1, 379, 1147, 635),
+                                   (3, 130, 70, 33), (1, 17, 40, 257)])
+def test_single_tf32_pass_is_exact_on_small_integers(forced, shape):
+    """Integers up to 2048 are exact in TF32 and the sums stay below 2^24, so even one
+    TF32 pass must reproduce the wrapping-free integer product exactly.  This isolates the
+    TMA maps, shared-memory descriptors and the TMEM read-back from the split arithmetic."""
+    B, N, K, M = shape
+    rng = np.random.default_rng(31)
+    a = rng.integers(-9, 10, (B, N, K)).astype(np.float32)
+    b = rng.integers(-9, 10, (B, K, M)).astype(np.float32)
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64)).astype(np.float32)
+    forced.set_option("tf32_terms", 1)
+    for name, (l, r) in layouts(dev(a), dev(b)).items():
+        got = host(forced.batched_matmul(l, r))
+        assert forced.last_variant() == forced.Variant.TCGEN05_3XTF32
+        assert np.array_equal(got, want), name
+    forced.check_device(0)
+
+
+@pytest.mark.parametrize("shape", [(1, 128, 128, 128), (1, 379, 1147, 635), (4, 200, 300, 150), (1, 512, 4096, 256)])
+def test_split_tf32_meets_f32_tolerance_all_layouts(forced, shape):
+    B, N, K, M = shape
+    rng = np.random.default_rng(32)
+    a = rng.standard_normal((B, N, K)).astype(np.float32)
+    b = rng.standard_normal((B, K, M)).astype(np.float32)
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    for name, (l, r) in layouts(dev(a), dev(b)).items():
+        got = host(forced.batched_matmul(l, r))
+        assert rel_to_max(got, want) <= F32_TOL, name
+    forced.check_device(0)
+
+
+def test_single_pass_is_not_enough_and_split_is(forced):
+    """The reason for the split: one TF32 pass misses 1e-5, three passes meet it."""
+    rng = np.random.default_rng(33)
+    a = rng.standard_normal((1, 256, 2048)).astype(np.float32)
+    b = rng.standard_normal((1, 2048, 256)).astype(np.float32)
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    forced.set_option("tf32_terms", 1)
+    one = rel_to_max(host(forced.batched_matmul(dev(a), dev(b))), want)
+    forced.set_option("tf32_terms", 3)
+    three = rel_to_max(host(forced.batched_matmul(dev(a), dev(b))), want)
+    assert one > F32_TOL
+    assert three <= F32_TOL
+
+
+def test_tensor_core_reads_fp32_words_as_truncated_tf32(forced):
+    """The split assumes kind::tf32 ignores the low 13 mantissa bits of an fp32 word.
+    Rewriting the raw tile with its explicitly masked big part must therefore not change
+    a single bit of the result."""
+    rng = np.random.default_rng(34)
+    a = rng.standard_normal((1, 256, 512)).astype(np.float32)
+    b = rng.standard_normal((1, 512, 256)).astype(np.float32)
+    plain = host(forced.batched_matmul(dev(a), dev(b)))
+    forced.set_option("mask_big", 1)
+    masked = host(forced.batched_matmul(dev(a), dev(b)))
+    assert np.array_equal(plain, masked)
+
+
+def test_long_k_accumulation_error(forced):
+    """K = 8192 (the headline shape's depth) on N(0, 1/sqrt(K)) entries."""
+    K = 8192
+    rng = np.random.default_rng(35)
+    a = (rng.standard_normal((1, 256, K)) * K ** -0.5).astype(np.float32)
+    b = (rng.standard_normal((1, K, 384)) * K ** -0.5).astype(np.float32)
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    got = host(forced.batched_matmul(dev(a), dev(b)))
+    assert rel_to_max(got, want) <= F32_TOL
+
+
+def test_broadcast_batch_and_offset_views(forced):
+    rng = np.random.default_rng(36)
+    a = rng.standard_normal((5, 128, 64)).astype(np.float32)
+    b = rng.standard_normal((1, 64, 256)).astype(np.float32)
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    got = host(forced.batched_matmul(dev(a), dev(b).expand(5, 64, 256)))
+    assert rel_to_max(got, want) <= F32_TOL
+    # offset view: rows 8.. of a larger matrix, columns 64..192 of a wider rhs
+    big = dev(rng.standard_normal((1, 300, 64)).astype(np.float32))
+    wide = dev(rng.standard_normal((1, 64, 512)).astype(np.float32))
+    l, r = big[:, 8:264, :], wide[:, :, 64:192]
+    want = np.matmul(host(l).astype(np.float64), host(r).astype(np.float64))
+    assert rel_to_max(host(forced.batched_matmul(l, r)), want) <= F32_TOL
+
+
+def test_strided_output(forced):
+    rng = np.random.default_rng(37)
+    a = dev(rng.standard_normal((1, 256, 128)).astype(np.float32))
+    b = dev(rng.standard_normal((1, 128, 512)).astype(np.float32))
+    C = torch.zeros((1, 256, 512), device="cuda")
+    for c0 in (0, 256):
+        forced.batched_matmul(a, b[:, :, c0:c0 + 256], out=C[:, :, c0:c0 + 256])
+    full = forced.batched_matmul(a, b)
+    assert torch.equal(C, full)
+
+
+def test_ineligible_view_is_refused_when_forced_and_rerouted_when_not(forced):
+    a = torch.randn((1, 64, 70), device="cuda")[:, :, ::2]  # inner step 2
+    b = torch.randn((1, 35, 64), device="cuda")
+    with pytest.raises(forced.TTBError):
+        forced.batched_matmul(a, b)
+    forced.set_option("force_variant", 0)
+    out = forced.batched_matmul(a, b)
+    assert forced.last_variant() in (forced.Variant.SIMT, forced.Variant.SIMT_SPLITK)
+    want = np.matmul(host(a).astype(np.float64), host(b).astype(np.float64))
+    assert rel_to_max(host(out), want) <= F32_TOL

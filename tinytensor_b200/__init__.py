@@ -1,0 +1,35 @@
+"""B200-native matmul backend for tinytensor: host-side mirror of the reference interface.
+
+The product is ``libttb.so`` (hand-written sm_100a CUDA behind a C ABI, see
+``include/ttb.h``).  This package is the thin host layer used by the tests and the
+benchmark: it loads the library with ctypes and mirrors the names, argument
+meaning and error behaviour of the reference's matmul path
+(``tinytensor::matmul`` -> ``BackendBase::batched_matmul``).  torch is used only
+for device memory, streams and ``torch.distributed``.
+
+There is no CPU or eager fallback: importing works without the library, but any
+compute call raises if ``libttb.so`` is missing.
+"""
+from .backend import (  # noqa: F401
+    TTBError,
+    Variant,
+    batched_matmul,
+    batched_matmul_host,
+    check_device,
+    get_option,
+    last_variant,
+    launch_count,
+    lib,
+    lib_path,
+    matmul,
+    set_option,
+    tma_eligible,
+    view_of,
+)
+from .partition import Partition, ShardedMatmul, partition  # noqa: F401
+
+__all__ = [
+    "TTBError", "Variant", "batched_matmul", "batched_matmul_host", "check_device", "get_option",
+    "last_variant", "launch_count", "lib", "lib_path", "matmul", "set_option", "tma_eligible",
+    "view_of", "Partition", "ShardedMatmul", "partition",
+]

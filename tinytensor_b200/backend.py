@@ -1,0 +1,307 @@
+"""ctypes binding of libttb.so and the host-side mirror of tinytensor's matmul entry.
+
+Mirrors (reference paths relative to the tinytensor tree):
+  * ``matmul``            -> tinytensor::matmul, tinytensor/tensor/tensor.cpp:2390-2484
+  * ``batched_matmul``    -> BackendCUDA::batched_matmul / cuda::batched_matmul_runner,
+                             tinytensor/tensor/backend/cuda/matmul.cu:26-78
+  * ``TTBError``          -> TTException, include/tt/exception.h:15-25
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import os
+from pathlib import Path
+
+import numpy as np
+import torch
+
+_PKG = Path(__file__).resolve().parent
+_LIB_NAME = "libttb.so"
+
+
+class TTBError(RuntimeError):
+    """Raised for every error the reference reports with TTException, and for any
+    non-zero status of the C ABI."""
+
+    def __init__(self, message: str, status: int = -1):
+        super().__init__(message)
+        self.status = status
+
+
+class Variant(enum.IntEnum):
+    AUTO = 0
+    SIMT = 1
+    TCGEN05_3XTF32 = 2
+    DMMA_F64 = 3
+    SIMT_SPLITK = 4
+    TCGEN05_2CTA = 5
+
+
+class _View(ctypes.Structure):
+    _fields_ = [
+        ("data", ctypes.c_void_p),
+        ("offset", ctypes.c_int64),
+        ("size", ctypes.c_int64 * 3),
+        ("stride", ctypes.c_int64 * 3),
+    ]
+
+
+# tinytensor::ScalarType values (include/tt/scalar.h:21-29).
+_DTYPE_CODE = {
+    torch.bool: 0,
+    torch.uint8: 1,
+    torch.int16: 2,
+    torch.int32: 3,
+    torch.int64: 4,
+    torch.float32: 5,
+    torch.float64: 6,
+}
+_NP_DTYPE_CODE = {
+    np.dtype(np.bool_): 0,
+    np.dtype(np.uint8): 1,
+    np.dtype(np.int16): 2,
+    np.dtype(np.int32): 3,
+    np.dtype(np.int64): 4,
+    np.dtype(np.float32): 5,
+    np.dtype(np.float64): 6,
+}
+# promote_type_map of the reference (tinytensor/common/scalar.cpp:17-26): the
+# promoted type is the one with the larger enum value.
+_CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
+
+_lib = None
+
+
+def lib_path() -> Path:
+    override = os.environ.get("TTB_LIBRARY")
+    return Path(override) if override else _PKG / _LIB_NAME
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libttb.so (once).  Raises if it has not been built: there is no fallback."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not path.exists():
+        raise TTBError(
+            f"{path} not found: build it with `python -m tinytensor_b200.build` "
+            "(this package has no CPU or eager fallback)"
+        )
+    L = ctypes.CDLL(str(path))
+    vp = ctypes.POINTER(_View)
+    L.ttb_batched_matmul.argtypes = [vp, vp, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    L.ttb_batched_matmul.restype = ctypes.c_int
+    L.ttb_batched_matmul_strided_out.argtypes = [
+        vp, vp, ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64), ctypes.c_int, ctypes.c_int,
+        ctypes.c_void_p,
+    ]
+    L.ttb_batched_matmul_strided_out.restype = ctypes.c_int
+    L.ttb_batched_matmul_host.argtypes = [vp, vp, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+    L.ttb_batched_matmul_host.restype = ctypes.c_int
+    L.ttb_partition.argtypes = [ctypes.c_int64] * 4 + [ctypes.c_int, ctypes.c_int, ctypes.c_int64,
+                                                      ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
+    L.ttb_partition.restype = ctypes.c_int
+    L.ttb_last_error.restype = ctypes.c_char_p
+    L.ttb_last_variant.restype = ctypes.c_int
+    L.ttb_launch_count.restype = ctypes.c_int64
+    L.ttb_variant_name.argtypes = [ctypes.c_int]
+    L.ttb_variant_name.restype = ctypes.c_char_p
+    L.ttb_set_option.argtypes = [ctypes.c_char_p, ctypes.c_int64]
+    L.ttb_set_option.restype = ctypes.c_int
+    L.ttb_get_option.argtypes = [ctypes.c_char_p]
+    L.ttb_get_option.restype = ctypes.c_int64
+    L.ttb_device_count.restype = ctypes.c_int
+    L.ttb_check_device.argtypes = [ctypes.c_int]
+    L.ttb_check_device.restype = ctypes.c_int
+    L.ttb_view_tma_eligible.argtypes = [vp, ctypes.c_int, ctypes.c_int]
+    L.ttb_view_tma_eligible.restype = ctypes.c_int
+    L.ttb_version.restype = ctypes.c_int
+    _lib = L
+    return L
+
+
+def _raise(status: int) -> None:
+    msg = lib().ttb_last_error().decode("utf-8", "replace")
+    raise TTBError(msg or f"ttb status {status}", status)
+
+
+def _make_view(data_ptr: int, offset: int, sizes, strides) -> _View:
+    v = _View()
+    v.data = data_ptr
+    v.offset = int(offset)
+    for i in range(3):
+        v.size[i] = int(sizes[i])
+        v.stride[i] = int(strides[i])
+    return v
+
+
+def view_of(t: torch.Tensor) -> _View:
+    """The (storage base, element offset, shape, element strides) of a rank-3 torch
+    tensor, i.e. the fields a tinytensor Tensor carries (include/tt/tensor.h:1570-1577)."""
+    if t.dim() != 3:
+        raise TTBError(f"expected a rank-3 tensor, got rank {t.dim()}")
+    return _make_view(t.untyped_storage().data_ptr(), t.storage_offset(), t.shape, t.stride())
+
+
+def set_option(key: str, value: int) -> None:
+    rc = lib().ttb_set_option(key.encode(), int(value))
+    if rc != 0:
+        _raise(rc)
+
+
+def get_option(key: str) -> int:
+    return int(lib().ttb_get_option(key.encode()))
+
+
+def last_variant() -> Variant:
+    return Variant(lib().ttb_last_variant())
+
+
+def launch_count() -> int:
+    return int(lib().ttb_launch_count())
+
+
+def check_device(device: int = 0) -> None:
+    """Synchronises `device` and raises if a bounded wait inside a kernel gave up."""
+    rc = lib().ttb_check_device(int(device))
+    if rc != 0:
+        _raise(rc)
+
+
+def tma_eligible(t: torch.Tensor, operand: int) -> bool:
+    v = view_of(t)
+    return bool(lib().ttb_view_tma_eligible(ctypes.byref(v), _DTYPE_CODE[t.dtype], operand))
+
+
+def _stream_ptr(stream) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return int(stream.cuda_stream)
+
+
+def batched_matmul(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """lhs[B,N,K] . rhs[B,K,M] -> [B,N,M] on the operands' CUDA device.
+
+    The backend operator of the reference (backend_base.h:130): rank-3 operands of one
+    dtype on one device, any strides; the result is a fresh contiguous tensor unless
+    `out` (rank 3, any strides) is given.  Queued on the current torch stream; does not
+    synchronise.
+    """
+    if lhs.dim() != 3 or rhs.dim() != 3:
+        raise TTBError(f"batched_matmul expects rank-3 operands, got {lhs.dim()} and {rhs.dim()}")
+    if lhs.device != rhs.device:
+        raise TTBError(f"Expected tensors to be on the same device. Given {lhs.device} and {rhs.device}")
+    if lhs.device.type != "cuda":
+        raise TTBError("tinytensor_b200 only runs on CUDA devices (no CPU fallback)")
+    if lhs.dtype != rhs.dtype:
+        raise TTBError(f"operands must share a dtype after promotion, got {lhs.dtype} and {rhs.dtype}")
+    if lhs.dtype not in _DTYPE_CODE:
+        raise TTBError(f"unsupported dtype {lhs.dtype}")
+    code = _DTYPE_CODE[lhs.dtype]
+    dev = lhs.device.index if lhs.device.index is not None else torch.cuda.current_device()
+    lv, rv = view_of(lhs), view_of(rhs)
+    L = lib()
+    if out is None:
+        if lhs.shape[0] != rhs.shape[0] or lhs.shape[2] != rhs.shape[1] or code == 0:
+            # Let the library produce the message; nothing is allocated or launched.
+            dummy = ctypes.c_void_p(8)
+            rc = L.ttb_batched_matmul(ctypes.byref(lv), ctypes.byref(rv), dummy, code, dev, None)
+            _raise(rc if rc != 0 else -1)
+        with torch.cuda.device(dev):
+            out = torch.empty((lhs.shape[0], lhs.shape[1], rhs.shape[2]), dtype=lhs.dtype, device=lhs.device)
+        rc = L.ttb_batched_matmul(ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.data_ptr()), code, dev,
+                                  ctypes.c_void_p(_stream_ptr(stream)))
+    else:
+        if out.dim() != 3 or tuple(out.shape) != (lhs.shape[0], lhs.shape[1], rhs.shape[2]):
+            raise TTBError(f"out has shape {tuple(out.shape)}, expected "
+                           f"{(lhs.shape[0], lhs.shape[1], rhs.shape[2])}")
+        if out.dtype != lhs.dtype or out.device != lhs.device:
+            raise TTBError("out must have the operands' dtype and device")
+        strides = (ctypes.c_int64 * 3)(*out.stride())
+        rc = L.ttb_batched_matmul_strided_out(
+            ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.untyped_storage().data_ptr()),
+            out.storage_offset(), strides, code, dev, ctypes.c_void_p(_stream_ptr(stream)))
+    if rc != 0:
+        _raise(rc)
+    return out
+
+
+def _promote(lhs: torch.Tensor, rhs: torch.Tensor):
+    if lhs.dtype not in _DTYPE_CODE or rhs.dtype not in _DTYPE_CODE:
+        raise TTBError("Unknown ScalarType")
+    code = max(_DTYPE_CODE[lhs.dtype], _DTYPE_CODE[rhs.dtype])
+    if code == 0:
+        raise TTBError(f"matmul does not support boolean tensors. Given {lhs.dtype} and {rhs.dtype}")
+    dt = _CODE_DTYPE[code]
+    # A cast yields a contiguous tensor in the reference too (backend/cuda/cast.cu:25-32).
+    return (lhs if lhs.dtype == dt else lhs.to(dt)), (rhs if rhs.dtype == dt else rhs.to(dt))
+
+
+def matmul(lhs: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
+    """tinytensor::matmul (tensor.cpp:2390-2484): dtype promotion, bool rejected, and the
+    five rank forms funnelled into one rank-3 batched product.  No broadcasting of batch
+    dims.  Unlike the reference, 2-D strided operands are passed as views (the reference's
+    reshape clones them first, tensor.cpp:1386); the values are the same."""
+    if lhs.device != rhs.device:
+        raise TTBError(f"Expected tensors to be on the same device. Given {lhs.device} and {rhs.device}")
+    lhs, rhs = _promote(lhs, rhs)
+    ld, rd = lhs.dim(), rhs.dim()
+    if ld == 1 and rd == 1:
+        if lhs.shape[0] != rhs.shape[0]:
+            raise TTBError(f"Invalid shapes for dot product. Both LHS and RHS must have same dimensions: "
+                           f"LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+        return batched_matmul(lhs.view(1, 1, -1) if lhs.is_contiguous() else lhs.unsqueeze(0).unsqueeze(0),
+                              rhs.unsqueeze(0).unsqueeze(2)).flatten()
+    if ld == 1 and rd == 2:
+        if lhs.shape[0] != rhs.shape[0]:
+            raise TTBError(f"Invalid shape for matrix multiplication. Length of LHS should equal size of RHS "
+                           f"dimension 0: LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+        return batched_matmul(lhs.unsqueeze(0).unsqueeze(0), rhs.unsqueeze(0)).flatten()
+    if ld == 2 and rd == 1:
+        if lhs.shape[1] != rhs.shape[0]:
+            raise TTBError(f"Invalid shape for matrix multiplication. Length of RHS should equal size of LHS "
+                           f"dimension 1: LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+        return batched_matmul(lhs.unsqueeze(0), rhs.unsqueeze(0).unsqueeze(2)).flatten()
+    if ld == 2 and rd == 2:
+        if lhs.shape[1] != rhs.shape[0]:
+            raise TTBError(f"Invalid shape for matrix multiplication. Size of LHS dimension 1 should equal size "
+                           f"of RHS dimension 0: LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+        return batched_matmul(lhs.unsqueeze(0), rhs.unsqueeze(0)).squeeze(0)
+    if ld == 3 and rd == 3:
+        if lhs.shape[2] != rhs.shape[1]:
+            raise TTBError(f"Invalid shape for batched matrix multiplication. Size of LHS dimension 2 should "
+                           f"equal size of RHS dimension 1: LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+        return batched_matmul(lhs, rhs)
+    raise TTBError("Unsupported sizes. Try reshaping or broadcasting. Expected dimensions of (LHS=1, RHS=1), "
+                   "(LHS=1, RHS=2), (LHS=2, RHS=1), (LHS=2, RHS=2) or (LHS=3, RHS=3).")
+
+
+def _np_view(a: np.ndarray) -> _View:
+    if a.ndim != 3:
+        raise TTBError(f"expected a rank-3 array, got rank {a.ndim}")
+    es = a.dtype.itemsize
+    if any(s % es or s < 0 for s in a.strides):
+        raise TTBError("array strides must be non-negative multiples of the element size")
+    return _make_view(a.ctypes.data, 0, a.shape, [s // es for s in a.strides])
+
+
+def batched_matmul_host(lhs: np.ndarray, rhs: np.ndarray, out: np.ndarray | None = None, device: int = 0) -> np.ndarray:
+    """Host-buffer form (ttb_batched_matmul_host): operands and result live in host memory;
+    the library copies in, multiplies on `device`, copies out and synchronises."""
+    if lhs.dtype != rhs.dtype:
+        raise TTBError("operands must share a dtype")
+    if lhs.dtype not in _NP_DTYPE_CODE:
+        raise TTBError(f"unsupported dtype {lhs.dtype}")
+    lv, rv = _np_view(lhs), _np_view(rhs)
+    shape = (lhs.shape[0], lhs.shape[1], rhs.shape[2])
+    if out is None:
+        out = np.empty(shape, dtype=lhs.dtype)
+    elif out.shape != shape or out.dtype != lhs.dtype or not out.flags.c_contiguous:
+        raise TTBError("out must be a C-contiguous array of the result shape and dtype")
+    rc = lib().ttb_batched_matmul_host(ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.ctypes.data),
+                                       _NP_DTYPE_CODE[lhs.dtype], int(device))
+    if rc != 0:
+        _raise(rc)
+    return out

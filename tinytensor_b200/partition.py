@@ -1,0 +1,152 @@
+"""Multi-GPU partitioner for the matmul path: one process per GPU, torch.distributed
+for the plumbing.
+
+The reference has no distributed layer at all; "multi-device" there is a
+``Device{backend,id}`` tag and a ``cudaSetDevice`` before each launch
+(include/tt/device.h:37-51, backend/cuda/kernel_launch.cuh:20), and a cross-device
+copy bounces through the host (autograd/unary_ops.cpp:67-83).  This module adds the
+one thing the matmul path needs on an 8-GPU box:
+
+* batched products (B > 1) are sharded over the batch dim -- batches are independent,
+  so there is no data-path collective; each rank keeps its slice of the result
+  (``gather=True`` all-gathers the slices, which are contiguous chunks of [B,N,M]);
+* a single large product (B == 1) is sharded over output-column blocks: rank r computes
+  ``lhs . rhs[:, c0:c1]`` -- a strided view of rhs consumed directly by the kernels --
+  into its column block of C, and one all-gather of C follows (the only exchange step).
+
+The split itself is computed by the C ABI (``ttb_partition``) so that the C++ shim
+and this module agree.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import backend
+
+# Column blocks are cut on multiples of the tensor-core kernel's tile width so that no
+# rank gets a partial tile in the middle of the matrix, and block starts stay 16-byte
+# aligned for TMA.
+COL_ALIGN = 128
+
+
+@dataclass(frozen=True)
+class Partition:
+    kind: str  # "batch" or "columns"
+    begin: int
+    end: int
+
+    @property
+    def size(self) -> int:
+        return self.end - self.begin
+
+
+def partition(B: int, N: int, K: int, M: int, world: int, rank: int, col_align: int = COL_ALIGN) -> Partition:
+    b, e = ctypes.c_int64(), ctypes.c_int64()
+    rc = backend.lib().ttb_partition(B, N, K, M, world, rank, col_align, ctypes.byref(b), ctypes.byref(e))
+    if rc < 0:
+        backend._raise(rc)
+    return Partition("columns" if rc == 1 else "batch", b.value, e.value)
+
+
+class ShardedMatmul:
+    """Callable ``(lhs, rhs) -> out`` that splits one batched product over the ranks of a
+    process group.  Every rank passes the FULL operands (replicated on its own device;
+    placing them is set-up, not part of the product) and computes only its share.
+
+    ``local_matmul(lhs3, rhs3, out3)`` does the per-rank product; it defaults to the CUDA
+    kernels and exists so the host logic can be exercised on CPU ranks (gloo) in tests.
+    """
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None,
+                 local_matmul: Optional[Callable[[torch.Tensor, torch.Tensor, torch.Tensor], None]] = None,
+                 col_align: int = COL_ALIGN):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.col_align = col_align
+        self._local = local_matmul or (lambda a, b, o: backend.batched_matmul(a, b, out=o))
+        self._stage: Optional[torch.Tensor] = None
+        self._gathered: Optional[torch.Tensor] = None
+
+    def plan(self, lhs: torch.Tensor, rhs: torch.Tensor) -> Partition:
+        B, N, K = lhs.shape
+        M = rhs.shape[2]
+        return partition(B, N, K, M, self.world, self.rank, self.col_align)
+
+    def _buffer(self, name: str, shape, like: torch.Tensor) -> torch.Tensor:
+        cur = getattr(self, name)
+        n = 1
+        for s in shape:
+            n *= s
+        if cur is None or cur.numel() < n or cur.dtype != like.dtype or cur.device != like.device:
+            cur = torch.empty(n, dtype=like.dtype, device=like.device)
+            setattr(self, name, cur)
+        return cur[:n].view(*shape)
+
+    def __call__(self, lhs: torch.Tensor, rhs: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 gather: bool = True) -> torch.Tensor:
+        if lhs.dim() != 3 or rhs.dim() != 3:
+            raise backend.TTBError("ShardedMatmul expects rank-3 operands")
+        B, N, K = lhs.shape
+        M = rhs.shape[2]
+        part = self.plan(lhs, rhs)
+        if part.kind == "batch":
+            return self._batch(lhs, rhs, out, part, gather)
+        return self._columns(lhs, rhs, out, part, gather)
+
+    # -- batch sharding: no exchange unless the caller wants the full result everywhere
+    def _batch(self, lhs, rhs, out, part: Partition, gather: bool):
+        B, N, _ = lhs.shape
+        M = rhs.shape[2]
+        if out is None:
+            out = torch.empty((B, N, M), dtype=lhs.dtype, device=lhs.device)
+        if part.size > 0:
+            self._local(lhs[part.begin:part.end], rhs[part.begin:part.end], out[part.begin:part.end])
+        if gather and self.world > 1:
+            # Slices are contiguous chunks of [B,N,M]; sizes may differ by one batch.
+            chunks = []
+            for r in range(self.world):
+                p = partition(B, N, lhs.shape[2], M, self.world, r, self.col_align)
+                chunks.append(out[p.begin:p.end])
+            if len({c.shape[0] for c in chunks}) == 1 and out.is_contiguous():
+                dist.all_gather_into_tensor(out.view(-1), chunks[self.rank].reshape(-1), group=self.group)
+            else:
+                for r, c in enumerate(chunks):
+                    if c.numel():
+                        dist.broadcast(c, src=dist.get_global_rank(self.group, r) if self.group else r,
+                                       group=self.group)
+        return out if gather or self.world == 1 else out[part.begin:part.end]
+
+    # -- column sharding: compute the block, then all-gather C
+    def _columns(self, lhs, rhs, out, part: Partition, gather: bool):
+        _, N, _ = lhs.shape
+        M = rhs.shape[2]
+        if out is None:
+            out = torch.empty((1, N, M), dtype=lhs.dtype, device=lhs.device)
+        if self.world == 1 or not gather:
+            if part.size > 0:
+                self._local(lhs, rhs[:, :, part.begin:part.end], out[:, :, part.begin:part.end])
+            return out
+        parts = [partition(1, N, lhs.shape[2], M, self.world, r, self.col_align) for r in range(self.world)]
+        width = max(p.size for p in parts)
+        equal = all(p.size == width for p in parts)
+        # NCCL concatenates contiguous per-rank chunks, so the block is computed into a
+        # contiguous [N, width] staging buffer, gathered as [world, N, width], and then laid
+        # out row-major.
+        stage = self._buffer("_stage", (1, N, width), lhs)
+        if part.size > 0:
+            self._local(lhs, rhs[:, :, part.begin:part.end], stage[:, :, :part.size])
+        gathered = self._buffer("_gathered", (self.world, N, width), lhs)
+        dist.all_gather_into_tensor(gathered.view(-1), stage.reshape(-1), group=self.group)
+        if equal:
+            out.view(N, self.world, width).copy_(gathered.permute(1, 0, 2))
+        else:
+            for r, p in enumerate(parts):
+                if p.size:
+                    out[0, :, p.begin:p.end].copy_(gathered[r, :, :p.size])
+        return out
