@@ -1,33 +1,45 @@
 // gemm_f32_tcgen05.cu -- f32 batched GEMM on the 5th-generation tensor cores of sm_100a.
 //
 // C[b] = A[b] . B[b] in fp32-class accuracy from three TF32 tensor-core products
-// ("3xTF32"): every fp32 operand x is split as x = big + small with
-// big = x with its low 13 mantissa bits cleared (what kind::tf32 reads from an fp32
-// word) and small = x - big (exact in fp32).  Then
-//     A.B ~= big_A.big_B + small_A.big_B + big_A.small_B
+// ("3xTF32").  kind::tf32 reads an fp32 word and ignores its low 13 mantissa bits, so
+// every operand x is split as x = big + small with big = x truncated to TF32 (which the
+// tensor core derives by itself from the raw word) and small = x - big (exact in fp32,
+// then rounded to nearest TF32).  Then
+//     A.B ~= small_A.big_B + big_A.small_B + big_A.big_B
 // and the dropped small.small term is below 2^-20 relative.
+//
+// The tensor core's fp32 accumulator does not round to nearest: summing all of a long K
+// inside TMEM loses accuracy in proportion to K.  K is therefore cut into chunks (default
+// 8 K-blocks = 256 elements); each chunk is accumulated in TMEM from zero and the chunk
+// sums are added in fp32 registers (round-to-nearest) by the epilogue warps.
 //
 // Replaces matmul_kernel<float> of the reference
 // (tinytensor/tensor/backend/cuda/kernel/matmul.cuh:27-151), a 64x64x8 CUDA-core
 // kernel that needs contiguous operands.
 //
-// Structure of one CTA (persistent, one per SM, static round-robin over tiles):
-//   warp 0      TMA producer: cp.async.bulk.tensor loads of the raw fp32 A and B
-//               tiles, through tensor maps built from the operand's own strides
-//               (K-major or MN-major, so transposed views need no copy);
-//   warps 6-9   converters: read the raw tile from shared memory, write the
-//               `small` tile (same offsets, so the swizzled layout is preserved),
-//               fence.proxy.async, signal;
-//   warp 1      MMA issuer: one thread issues tcgen05.mma kind::tf32, three per
-//               K step, accumulating in TMEM; tcgen05.commit releases the stage;
-//   warps 2-5   epilogue: tcgen05.ld the accumulator, store C.  Two TMEM
-//               accumulators, so the epilogue of tile i overlaps the mainloop of
-//               tile i+1.
-// All waits are bounded: a wait that gives up writes an error word and the CTA
-// unwinds (TMEM freed) instead of hanging.
+// One CTA (persistent, static round-robin over tiles), roles by aligned warpgroup:
+//   warp 0       TMA producer: cp.async.bulk.tensor loads of the raw fp32 A and B tiles
+//                through tensor maps built from the operand's own strides (K-major or
+//                MN-major, so transposed views need no copy);
+//   warp 1       MMA issuer: one thread issues tcgen05.mma kind::tf32, three per K step,
+//                accumulating in TMEM; tcgen05.commit releases the stage / publishes the
+//                accumulator.  Warps 2-3 idle.
+//   epilogue WG  (one per 128 accumulator columns): tcgen05.ld each chunk sum, add into
+//                registers, store C after the last chunk.  Two TMEM accumulators, so the
+//                read-out of chunk i overlaps the MMAs of chunk i+1.
+//   last WG      converters: read the raw tile from shared memory, write the `small` tile
+//                at the same offsets (the swizzled layout is preserved),
+//                fence.proxy.async, signal.
+// Two forms: CG = 1, a 128x128 tile per CTA; CG = 2, a 256x256 tile per CTA pair
+// (cta_group::2): each CTA loads 128 rows of A and 128 columns of B and owns 128 rows of
+// the accumulator, which halves shared-memory and L2 traffic per flop.  No load carries a
+// multicast qualifier; each CTA fetches its own tiles.
+// All waits are bounded: a wait that gives up writes an error word and the CTA unwinds
+// (TMEM freed) instead of hanging.
 #include <cuda.h>
 
 #include <cstdio>
+#include <cstring>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -48,13 +60,23 @@ constexpr int RAW_BYTES = 2 * TILE_BYTES;      // raw A + raw B
 constexpr int STAGE_BYTES = 2 * RAW_BYTES;     // + small A + small B
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
 constexpr int MN_BOX_BYTES = 32 * BK * 4;      // one MN-major TMA box: 32 (MN) x BK (K)
+constexpr int DEFAULT_K_CHUNK = 8;             // K blocks summed inside TMEM
 
-constexpr int NUM_EPI_WARPS = 4;
-constexpr int NUM_CONV_WARPS = 4;
-constexpr int NUM_WARPS = 2 + NUM_EPI_WARPS + NUM_CONV_WARPS;
-constexpr int NUM_THREADS = NUM_WARPS * 32;
-constexpr int FIRST_EPI_WARP = 2;
-constexpr int FIRST_CONV_WARP = 2 + NUM_EPI_WARPS;
+template <int CG>
+struct Cfg {
+    static constexpr int EPI_WGS = CG;                 // one epilogue warpgroup per 128 columns
+    static constexpr int NUM_WARPS = 4 * (2 + EPI_WGS);
+    static constexpr int NUM_THREADS = NUM_WARPS * 32;
+    static constexpr int FIRST_EPI_WARP = 4;
+    static constexpr int FIRST_CONV_WARP = 4 + 4 * EPI_WGS;
+    static constexpr int NUM_CONV_WARPS = 4;
+    static constexpr int UMMA_M = BM * CG;
+    static constexpr int UMMA_N = BNC * CG;
+    static constexpr int ACC_COLS = UMMA_N;            // fp32 columns of one accumulator
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;     // two accumulators
+    static constexpr int TILE_M = BM * CG;             // rows of C per CTA (pair)
+    static constexpr int TILE_N = BNC * CG;
+};
 
 struct alignas(64) TcArgs {
     CUtensorMap tmap_a;
@@ -66,6 +88,7 @@ struct alignas(64) TcArgs {
     int a_batch_mul, b_batch_mul;
     int tiles_m, tiles_n, total_tiles;
     int terms;     // 3 = split-TF32, 1 = single pass (test only)
+    int k_chunk;   // K blocks per TMEM accumulation chunk
     int mask_big;  // converters also overwrite the raw tile with its masked big part
     DeviceStatus *status;
 };
@@ -77,7 +100,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 // Bounded wait that also leaves early when another role of this CTA gave up.
-// Time limit: 2 s of %globaltimer.
+// Time limit: 2 s of %globaltimer.  CLUSTER selects the cluster-scope acquire, needed
+// when arrivals come from the peer CTA.
 template <bool CLUSTER>
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
     unsigned long long t0 = 0;
@@ -116,28 +140,28 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 }
 
 template <int CG>
-__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const __grid_constant__ TcArgs args) {
-    static_assert(CG == 1, "only the single-CTA form is built here");
-    constexpr int UMMA_N = BNC * CG;
-    constexpr int ACC_COLS = UMMA_N;          // fp32 columns of one accumulator
-    constexpr int TMEM_COLS = 2 * ACC_COLS;   // two accumulators
+__global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const __grid_constant__ TcArgs args) {
+    using C = Cfg<CG>;
+    constexpr bool PAIR = CG == 2;
 
     extern __shared__ uint8_t smem_dyn[];
-    __shared__ uint64_t full_bar[STAGES];   // TMA bytes landed
-    __shared__ uint64_t conv_bar[STAGES];   // small tiles written
-    __shared__ uint64_t empty_bar[STAGES];  // MMAs that read the stage are done
-    __shared__ uint64_t acc_full_bar[2];
-    __shared__ uint64_t acc_empty_bar[2];
+    __shared__ uint64_t full_bar[STAGES];   // TMA bytes landed (local)
+    __shared__ uint64_t conv_bar[STAGES];   // small tiles written (lives in the leader CTA)
+    __shared__ uint64_t empty_bar[STAGES];  // MMAs that read the stage are done (local)
+    __shared__ uint64_t acc_full_bar[2];    // accumulator chunk complete (local)
+    __shared__ uint64_t acc_empty_bar[2];   // accumulator read out (lives in the leader CTA)
     __shared__ uint64_t drain_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = cta_rank == 0;
     volatile int *abort_flag = &abort_flag_s;
 
-    // 1024-byte alignment of the tile area in the shared window (needed by the
-    // 128-byte swizzle: the XOR pattern repeats every 8 rows of 128 bytes).
+    // 1024-byte alignment of the tile area in the shared window (the swizzle patterns
+    // repeat every 1024 bytes).
     const uint32_t dyn_base = smem_u32(smem_dyn);
     const uint32_t tiles_base = (dyn_base + 1023u) & ~1023u;
     uint8_t *tiles = smem_dyn + (tiles_base - dyn_base);
@@ -145,12 +169,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const _
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&conv_bar[s], NUM_CONV_WARPS);
+            mbar_init(&conv_bar[s], C::NUM_CONV_WARPS * CG);
             mbar_init(&empty_bar[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full_bar[a], 1);
-            mbar_init(&acc_empty_bar[a], NUM_EPI_WARPS);
+            mbar_init(&acc_empty_bar[a], 4 * C::EPI_WGS * CG);
         }
         mbar_init(&drain_bar, 1);
         abort_flag_s = 0;
@@ -159,19 +183,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const _
         tma_prefetch_desc(&args.tmap_b);
     }
     if (warp == 1) {
-        tmem_alloc<CG>(&tmem_base_slot, TMEM_COLS);
+        tmem_alloc<CG>(&tmem_base_slot, C::TMEM_COLS);
         tmem_relinquish<CG>();
     }
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) {
+        // The peer's barriers must be initialised before anything arrives on them.
+        cluster_arrive();
+        cluster_wait();
+    }
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
     const int num_kb = (args.K + BK - 1) / BK;
-    const int first_tile = blockIdx.x;
-    const int tile_step = gridDim.x;
+    const int k_chunk = args.k_chunk > 0 ? args.k_chunk : num_kb;
+    const int num_chunks = (num_kb + k_chunk - 1) / k_chunk;
+    const int first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+    const int tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
-    if (warp == 0) {
+    // Register budget per warpgroup (CTA-pair form: 512 threads start with 128 registers
+    // each; the epilogue holds 128 accumulators per thread and takes registers the other
+    // roles give up).  Each role's branch starts with its own setmaxnreg so that the
+    // compiler allocates that branch against its own budget.
+    if (warp < C::FIRST_EPI_WARP) {
+      if constexpr (PAIR) setmaxnreg_dec<64>();
+      if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int stage = 0;
@@ -181,9 +218,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const _
             for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
                 int b, tm, tn;
                 tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
-                const int m0 = tm * BM, n0 = tn * BNC;
+                const int m0 = tm * C::TILE_M + static_cast<int>(cta_rank) * BM;
+                const int n0 = tn * C::TILE_N + static_cast<int>(cta_rank) * BNC;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!wait_or_abort<false>(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                    if (!wait_or_abort<PAIR>(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         report(args.status, abort_flag, kErrProducerWait, static_cast<unsigned>(stage));
                         ok = false;
                         break;
@@ -223,132 +261,171 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const _
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc_tf32(BM * CG, UMMA_N, args.a_mn_major, args.b_mn_major);
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            const uint32_t idesc = make_idesc_tf32(C::UMMA_M, C::UMMA_N, args.a_mn_major, args.b_mn_major);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            // Descriptor fields per operand major.
-            //  K-major : rows of 128 B, 8-row groups 1024 B apart (SBO); a K step of 8
-            //            fp32 advances the start address by 32 B inside the swizzle row.
-            //  MN-major: 32-element (128 B) MN groups MN_BOX_BYTES apart (LBO), 8-row K
-            //            groups 1024 B apart (SBO); a K step advances by 1024 B.
-            const uint32_t a_lbo = args.a_mn_major ? MN_BOX_BYTES : 16, a_kstep = args.a_mn_major ? 1024 : 32;
-            const uint32_t b_lbo = args.b_mn_major ? MN_BOX_BYTES : 16, b_kstep = args.b_mn_major ? 1024 : 32;
+            // Shared-memory descriptor fields per operand major.
+            //  K-major : 128-byte swizzle (16 B chunks); rows of 128 B, 8-row groups 1024 B
+            //            apart (SBO); a K step of 8 fp32 advances the start address by 32 B
+            //            inside the swizzle row.
+            //  MN-major: 128-byte swizzle with 32 B chunks (the only layout tcgen05.mma takes
+            //            for MN-major tf32); a 32-element MN group is MN_BOX_BYTES from the next
+            //            (LBO), 4-row K groups are 512 B apart (SBO); a K step of 8 rows
+            //            advances by 1024 B.
+            const uint32_t a_lbo = args.a_mn_major ? MN_BOX_BYTES : 16, a_sbo = args.a_mn_major ? 512 : 1024;
+            const uint32_t a_kstep = args.a_mn_major ? 1024 : 32;
+            const uint64_t a_swz = args.a_mn_major ? kSwizzle128Base32 : kSwizzle128;
+            const uint32_t b_lbo = args.b_mn_major ? MN_BOX_BYTES : 16, b_sbo = args.b_mn_major ? 512 : 1024;
+            const uint32_t b_kstep = args.b_mn_major ? 1024 : 32;
+            const uint64_t b_swz = args.b_mn_major ? kSwizzle128Base32 : kSwizzle128;
+            uint32_t peer_empty[STAGES], peer_acc_full[2];
+            if constexpr (PAIR) {
+                for (int s = 0; s < STAGES; ++s) peer_empty[s] = mapa(smem_u32(&empty_bar[s]), 1);
+                for (int a = 0; a < 2; ++a) peer_acc_full[a] = mapa(smem_u32(&acc_full_bar[a]), 1);
+            }
             for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
-                if (!wait_or_abort<false>(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
-                    report(args.status, abort_flag, kErrAccEmptyWait, static_cast<unsigned>(acc));
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_COLS);
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!wait_or_abort<false>(&conv_bar[stage], phase, abort_flag) ||
-                        !wait_or_abort<false>(&full_bar[stage], phase, abort_flag)) {
-                        report(args.status, abort_flag, kErrMmaWait, static_cast<unsigned>(stage));
+                for (int ch = 0; ch < num_chunks && ok; ++ch) {
+                    if (!wait_or_abort<PAIR>(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
+                        report(args.status, abort_flag, kErrAccEmptyWait, static_cast<unsigned>(acc));
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t a_raw = tiles_base + stage * STAGE_BYTES;
-                    const uint32_t b_raw = a_raw + TILE_BYTES;
-                    const uint32_t a_small = a_raw + RAW_BYTES;
-                    const uint32_t b_small = b_raw + RAW_BYTES;
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * C::ACC_COLS);
+                    const int kb_begin = ch * k_chunk;
+                    const int kb_end = (kb_begin + k_chunk < num_kb) ? kb_begin + k_chunk : num_kb;
+                    for (int kb = kb_begin; kb < kb_end; ++kb) {
+                        if (!wait_or_abort<PAIR>(&conv_bar[stage], phase, abort_flag)) {
+                            report(args.status, abort_flag, kErrMmaWait, static_cast<unsigned>(stage));
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t a_raw = tiles_base + stage * STAGE_BYTES;
+                        const uint32_t b_raw = a_raw + TILE_BYTES;
+                        const uint32_t a_small = a_raw + RAW_BYTES;
+                        const uint32_t b_small = b_raw + RAW_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        const uint64_t da_big = make_smem_desc(a_raw + kk * a_kstep, a_lbo, 1024, kSwizzle128);
-                        const uint64_t db_big = make_smem_desc(b_raw + kk * b_kstep, b_lbo, 1024, kSwizzle128);
-                        if (args.terms == 3) {
-                            const uint64_t da_small =
-                                make_smem_desc(a_small + kk * a_kstep, a_lbo, 1024, kSwizzle128);
-                            const uint64_t db_small =
-                                make_smem_desc(b_small + kk * b_kstep, b_lbo, 1024, kSwizzle128);
-                            // Small terms first: they are ~2^-11 of the big term.
-                            mma_tf32<CG>(d_tmem, da_small, db_big, idesc, (kb | kk) != 0);
-                            mma_tf32<CG>(d_tmem, da_big, db_small, idesc, 1);
-                            mma_tf32<CG>(d_tmem, da_big, db_big, idesc, 1);
-                        } else {
-                            mma_tf32<CG>(d_tmem, da_big, db_big, idesc, (kb | kk) != 0);
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                            const uint32_t fresh = (kb != kb_begin || kk != 0) ? 1u : 0u;
+                            const uint64_t da_big = make_smem_desc(a_raw + kk * a_kstep, a_lbo, a_sbo, a_swz);
+                            const uint64_t db_big = make_smem_desc(b_raw + kk * b_kstep, b_lbo, b_sbo, b_swz);
+                            if (args.terms == 3) {
+                                const uint64_t da_small = make_smem_desc(a_small + kk * a_kstep, a_lbo, a_sbo, a_swz);
+                                const uint64_t db_small = make_smem_desc(b_small + kk * b_kstep, b_lbo, b_sbo, b_swz);
+                                // Small terms first: they are ~2^-11 of the big term.
+                                mma_tf32<CG>(d_tmem, da_small, db_big, idesc, fresh);
+                                mma_tf32<CG>(d_tmem, da_big, db_small, idesc, 1);
+                                mma_tf32<CG>(d_tmem, da_big, db_big, idesc, 1);
+                            } else {
+                                mma_tf32<CG>(d_tmem, da_big, db_big, idesc, fresh);
+                            }
+                        }
+                        mma_commit<CG>(smem_u32(&empty_bar[stage]));
+                        if constexpr (PAIR) mma_commit<CG>(peer_empty[stage]);
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
                         }
                     }
-                    mma_commit<CG>(smem_u32(&empty_bar[stage]));
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
+                    if (!ok) break;
+                    mma_commit<CG>(smem_u32(&acc_full_bar[acc]));
+                    if constexpr (PAIR) mma_commit<CG>(peer_acc_full[acc]);
+                    acc ^= 1;
+                    if (acc == 0) acc_phase ^= 1u;
                 }
-                if (!ok) break;
-                mma_commit<CG>(smem_u32(&acc_full_bar[acc]));
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
             }
             // Everything issued must have retired before TMEM is freed.
             mma_commit<CG>(smem_u32(&drain_bar));
             for (int i = 0; i < 1000000; ++i)
                 if (mbar_try_wait(&drain_bar, 0)) break;
         }
-    } else if (warp < FIRST_CONV_WARP) {
+      }
+    } else if (warp < C::FIRST_CONV_WARP) {
         // ------------------------------------------------------------ epilogue
-        const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, +32)
+        if constexpr (PAIR) setmaxnreg_inc<184>();
+        const int quarter = warp & 3;                         // TMEM lanes [32*quarter, +32)
+        const int col_half = (warp - C::FIRST_EPI_WARP) >> 2;  // which 128 accumulator columns
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         const bool vec_ok = args.c_sj == 1 && (args.c_si & 3) == 0 && (args.c_sb & 3) == 0 &&
                             (reinterpret_cast<uintptr_t>(args.c) & 15) == 0;
+        uint32_t acc_empty_remote[2] = {0, 0};
+        if constexpr (PAIR) {
+            for (int a = 0; a < 2; ++a) acc_empty_remote[a] = mapa(smem_u32(&acc_empty_bar[a]), 0);
+        }
+        float sum[128];
         for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
             int b, tm, tn;
             tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
-            if (!wait_or_abort<false>(&acc_full_bar[acc], acc_phase, abort_flag)) {
-                if (lane == 0) report(args.status, abort_flag, kErrEpilogueWait, static_cast<unsigned>(acc));
-                ok = false;
-                break;
-            }
-            tc_fence_after_sync();
-            const int row = tm * BM + quarter * 32 + lane;
-            const int n0 = tn * BNC;
-            float *crow = args.c + static_cast<long long>(b) * args.c_sb + static_cast<long long>(row) * args.c_si;
-            const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * ACC_COLS) +
-                                   (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-            for (int ch = 0; ch < BNC / 32; ++ch) {
-                const int col0 = n0 + ch * 32;
-                if (col0 >= args.M) break;  // warp-uniform
-                uint32_t v[32];
-                tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
-                tmem_ld_wait();
-                if (row < args.N) {
-                    if (vec_ok && col0 + 32 <= args.M) {
-                        float4 *dst = reinterpret_cast<float4 *>(crow + col0);
+            for (int ch = 0; ch < num_chunks; ++ch) {
+                if (!wait_or_abort<PAIR>(&acc_full_bar[acc], acc_phase, abort_flag)) {
+                    if (lane == 0) report(args.status, abort_flag, kErrEpilogueWait, static_cast<unsigned>(acc));
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * C::ACC_COLS + col_half * 128) +
+                                       (static_cast<uint32_t>(quarter * 32) << 16);
+                const bool first = ch == 0;
 #pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            dst[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
-                                                 __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
-                    } else {
+                for (int q = 0; q < 8; ++q) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(t_row + static_cast<uint32_t>(q * 16), v);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < args.M)
-                                crow[static_cast<long long>(col0 + j) * args.c_sj] = __uint_as_float(v[j]);
+                    for (int j = 0; j < 16; ++j) {
+                        const float x = __uint_as_float(v[j]);
+                        sum[q * 16 + j] = first ? x : sum[q * 16 + j] + x;
                     }
                 }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (PAIR)
+                        mbar_arrive_cluster(acc_empty_remote[acc]);
+                    else
+                        mbar_arrive(&acc_empty_bar[acc]);
+                }
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1u;
+            if (!ok) break;
+            const int row = tm * C::TILE_M + static_cast<int>(cta_rank) * BM + quarter * 32 + lane;
+            const int col0 = tn * C::TILE_N + col_half * 128;
+            if (row < args.N && col0 < args.M) {
+                float *crow = args.c + static_cast<long long>(b) * args.c_sb + static_cast<long long>(row) * args.c_si;
+                if (vec_ok && col0 + 128 <= args.M) {
+                    float4 *dst = reinterpret_cast<float4 *>(crow + col0);
+#pragma unroll
+                    for (int q = 0; q < 32; ++q)
+                        dst[q] = make_float4(sum[4 * q], sum[4 * q + 1], sum[4 * q + 2], sum[4 * q + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 128; ++j)
+                        if (col0 + j < args.M) crow[static_cast<long long>(col0 + j) * args.c_sj] = sum[j];
+                }
+            }
         }
     } else {
         // ------------------------------------------------------------ converters
-        const int ctid = threadIdx.x - FIRST_CONV_WARP * 32;
-        constexpr int NCT = NUM_CONV_WARPS * 32;
+        if constexpr (PAIR) setmaxnreg_dec<72>();
+        const int ctid = threadIdx.x - C::FIRST_CONV_WARP * 32;
+        constexpr int NCT = C::NUM_CONV_WARPS * 32;
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
         const bool mask_big = args.mask_big != 0;
+        uint32_t conv_remote[STAGES] = {0, 0, 0};
+        if constexpr (PAIR) {
+            for (int s = 0; s < STAGES; ++s) conv_remote[s] = mapa(smem_u32(&conv_bar[s]), 0);
+        }
         for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
             for (int kb = 0; kb < num_kb; ++kb) {
                 if (!wait_or_abort<false>(&full_bar[stage], phase, abort_flag)) {
@@ -366,16 +443,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const _
                     big.y = x.y & 0xFFFFE000u;
                     big.z = x.z & 0xFFFFE000u;
                     big.w = x.w & 0xFFFFE000u;
-                    sm.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(big.x));
-                    sm.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(big.y));
-                    sm.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(big.z));
-                    sm.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(big.w));
+                    // small = x - big is exact; + 0x1000 on its bits rounds it to the nearest
+                    // TF32 value once the tensor core drops the low 13 bits.
+                    sm.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(big.x)) + 0x1000u;
+                    sm.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(big.y)) + 0x1000u;
+                    sm.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(big.z)) + 0x1000u;
+                    sm.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(big.w)) + 0x1000u;
                     small[i] = sm;
                     if (mask_big) raw[i] = big;
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&conv_bar[stage]);
+                if (lane == 0) {
+                    if constexpr (PAIR)
+                        mbar_arrive_cluster(conv_remote[stage]);
+                    else
+                        mbar_arrive(&conv_bar[stage]);
+                }
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
@@ -387,10 +471,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const _
     // ---------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) {
+        // Neither CTA may leave while its peer can still signal its barriers or the
+        // pair's MMAs can still write its TMEM.
+        cluster_arrive();
+        cluster_wait();
+    }
     if (warp == 1) {
         __syncwarp();
         tc_fence_after_sync();
-        tmem_dealloc<CG>(tmem_base, TMEM_COLS);
+        tmem_dealloc<CG>(tmem_base, C::TMEM_COLS);
     }
 }
 
@@ -423,6 +513,54 @@ bool plan(const Problem &p, TcPlan *pl, char *why, int why_len) {
         return false;
     }
     return true;
+}
+
+template <int CG>
+int launch_cg(const Problem &p, TcArgs &args, int sms) {
+    using C = Cfg<CG>;
+    args.tiles_m = static_cast<int>((p.N + C::TILE_M - 1) / C::TILE_M);
+    args.tiles_n = static_cast<int>((p.M + C::TILE_N - 1) / C::TILE_N);
+    args.total_tiles = args.tiles_m * args.tiles_n * args.B;
+    static bool attr_set[64] = {false};
+    auto kernel = gemm_f32_3xtf32_kernel<CG>;
+    if (!attr_set[p.device & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
+        attr_set[p.device & 63] = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(C::NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = p.stream;
+    cudaLaunchAttribute attr[1];
+    int units = sms / CG;  // CTAs (CG = 1) or CTA pairs (CG = 2) resident at once
+    if (CG == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        static int max_clusters[64] = {0};
+        if (max_clusters[p.device & 63] == 0) {
+            cfg.gridDim = dim3(static_cast<unsigned>(2 * units));
+            int n = 0;
+            cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveClusters");
+            if (n < 1) {
+                set_error("no CTA pair of the tcgen05 kernel fits on device %d", p.device);
+                return TTB_ECUDA;
+            }
+            max_clusters[p.device & 63] = n;
+        }
+        if (units > max_clusters[p.device & 63]) units = max_clusters[p.device & 63];
+    }
+    if (units > args.total_tiles) units = args.total_tiles;
+    cfg.gridDim = dim3(static_cast<unsigned>(units * CG));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
+    if (e != cudaSuccess) return cuda_fail(e, "gemm_f32_3xtf32_kernel launch");
+    note_launch(CG == 2 ? TTB_VARIANT_TCGEN05_2CTA : TTB_VARIANT_TCGEN05_3XTF32, 1);
+    return TTB_OK;
 }
 
 }  // namespace
@@ -458,28 +596,16 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt) {
     args.B = static_cast<int>(p.B);
     args.a_mn_major = pl.a_major == kMajorMN;
     args.b_mn_major = pl.b_major == kMajorMN;
-    args.tiles_m = static_cast<int>((p.N + BM - 1) / BM);
-    args.tiles_n = static_cast<int>((p.M + BNC - 1) / BNC);
-    args.total_tiles = args.tiles_m * args.tiles_n * args.B;
     args.terms = opt.terms;
+    args.k_chunk = opt.k_chunk > 0 ? opt.k_chunk : DEFAULT_K_CHUNK;
+    if (opt.k_chunk < 0) args.k_chunk = 0;  // whole K inside TMEM (test only)
     args.mask_big = opt.mask_big;
     int rc = device_status_ptr(p.device, &args.status);
     if (rc != TTB_OK) return rc;
     int sms = 148;
     sm_count(p.device, &sms);
-    static bool attr_set[64] = {false};
-    if (!attr_set[p.device & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_f32_3xtf32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             SMEM_BYTES);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
-        attr_set[p.device & 63] = true;
-    }
-    const int grid = args.total_tiles < sms ? args.total_tiles : sms;
-    gemm_f32_3xtf32_kernel<1><<<grid, NUM_THREADS, SMEM_BYTES, p.stream>>>(args);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "gemm_f32_3xtf32_kernel launch");
-    note_launch(TTB_VARIANT_TCGEN05_3XTF32, 1);
-    return TTB_OK;
+    if (opt.two_cta) return launch_cg<2>(p, args, sms);
+    return launch_cg<1>(p, args, sms);
 }
 
 }  // namespace ttb

@@ -245,8 +245,28 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
         : "r"(taddr)
         : "memory");
 }
+// Same, 16 columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Per-warpgroup register budget (all four warps of an aligned warpgroup execute it).
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ---------------------------------------------------------------- descriptors
@@ -254,8 +274,9 @@ __device__ __forceinline__ void tmem_ld_wait() {
 //   [ 0,14) start address >> 4      [16,30) leading byte offset >> 4
 //   [32,46) stride byte offset >> 4 [46,48) version = 1 on sm_100
 //   [49,52) base offset = 0 (tiles are 1024-byte aligned)
-//   [61,64) swizzle: 0 none, 2 = 128 B, 4 = 64 B, 6 = 32 B
+//   [61,64) swizzle: 0 none, 1 = 128 B span with 32 B chunks, 2 = 128 B, 4 = 64 B, 6 = 32 B
 constexpr uint64_t kSwizzle128 = 2;
+constexpr uint64_t kSwizzle128Base32 = 1;
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                                    uint64_t swizzle) {
     uint64_t d = 0;

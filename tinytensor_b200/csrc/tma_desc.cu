@@ -85,8 +85,13 @@ int encode_operand_tmap(CUtensorMap *map, const OperandView &v, OperandMajor maj
     gdim[2] = bcast ? 1 : static_cast<cuuint64_t>(v.batch);
     gstr[1] = bcast ? gstr[0] * gdim[1] : static_cast<cuuint64_t>(v.s_b) * es;
     box[2] = 1;
+    // K-major tiles use the ordinary 128-byte swizzle (16-byte chunks).  MN-major tiles of
+    // 32-bit elements must use the 128-byte swizzle with 32-byte chunks: it is the only
+    // shared-memory layout tcgen05.mma accepts for MN-major tf32 operands.
+    const CUtensorMapSwizzle swz =
+        (major == kMajorMN && es == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
     CUresult r = fn(map, dt, 3, const_cast<void *>(v.ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         if (why)

@@ -6,7 +6,9 @@
 // and the K dim, plus the batch dim:
 //   K-major  : K has element stride 1  -> map dims {K, MN, B}, box {32, rows, 1}
 //   MN-major : MN has element stride 1 -> map dims {MN, K, B}, box {32, 32, 1}
-// Both use the 128-byte swizzle; 32 fp32 = 128 bytes is one swizzle row.
+// Both use a 128-byte swizzle span (32 fp32 = one swizzle row): K-major tiles with
+// 16-byte chunks, MN-major fp32 tiles with 32-byte chunks (the layout tcgen05.mma
+// requires for MN-major tf32 operands).
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>

@@ -447,7 +447,7 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         return TTB_OK;
     }
     if (!strcmp(key, "k_chunk")) {
-        if (value < 0 || value > (1 << 20)) {
+        if (value < -1 || value > (1 << 20)) {
             set_error("k_chunk out of range");
             return TTB_EINVAL;
         }
