@@ -139,7 +139,8 @@ TTB_API const char *ttb_variant_name(int variant);
  * "tf32_terms" (3 = split-TF32, default; 1 = single TF32 pass, test only),
  * "k_chunk" (32-element K blocks accumulated inside the tensor core before the
  * partial sum is folded into fp32 registers; 0 = default of 8, -1 = whole K,
- * test only), "two_cta" (1 = automatic dispatch uses the CTA-pair kernel),
+ * test only), "two_cta" (automatic dispatch: -1 = pick the CTA-pair kernel by
+ * shape, default; 0 = never; 1 = always),
  * "splitk" (0 = never split K in the SIMT kernel), "mask_big" (test only).
  * Returns TTB_EINVAL for an unknown key or value. */
 TTB_API int ttb_set_option(const char *key, int64_t value);

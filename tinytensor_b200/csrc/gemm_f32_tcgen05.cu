@@ -54,11 +54,13 @@ constexpr int BM = 128;              // lhs rows per CTA
 constexpr int BNC = 128;             // rhs columns loaded per CTA
 constexpr int BK = 32;               // fp32 per K block = 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;            // K of one tcgen05.mma kind::tf32
-constexpr int STAGES = 3;
+constexpr int STAGES = 5;             // raw ring: tiles as TMA delivers them (deep: hides load latency)
+constexpr int SMALL_STAGES = 2;       // small ring: written by the converters just ahead of the MMAs
 constexpr int TILE_BYTES = BM * BK * 4;        // 16 KiB: one operand tile
 constexpr int RAW_BYTES = 2 * TILE_BYTES;      // raw A + raw B
-constexpr int STAGE_BYTES = 2 * RAW_BYTES;     // + small A + small B
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
+constexpr int STAGE_BYTES = RAW_BYTES;         // one slot of either ring
+constexpr int SMALL_RING_OFFSET = STAGES * STAGE_BYTES;
+constexpr int SMEM_BYTES = (STAGES + SMALL_STAGES) * STAGE_BYTES + 1024;  // + alignment slack
 constexpr int MN_BOX_BYTES = 32 * BK * 4;      // one MN-major TMA box: 32 (MN) x BK (K)
 constexpr int DEFAULT_K_CHUNK = 8;             // K blocks summed inside TMEM
 
@@ -146,8 +148,9 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 
     extern __shared__ uint8_t smem_dyn[];
     __shared__ uint64_t full_bar[STAGES];   // TMA bytes landed (local)
-    __shared__ uint64_t conv_bar[STAGES];   // small tiles written (lives in the leader CTA)
-    __shared__ uint64_t empty_bar[STAGES];  // MMAs that read the stage are done (local)
+    __shared__ uint64_t empty_bar[STAGES];  // MMAs that read the raw slot are done (local)
+    __shared__ uint64_t conv_bar[SMALL_STAGES];         // small tiles written (lives in the leader CTA)
+    __shared__ uint64_t small_empty_bar[SMALL_STAGES];  // MMAs that read the small slot are done (local)
     __shared__ uint64_t acc_full_bar[2];    // accumulator chunk complete (local)
     __shared__ uint64_t acc_empty_bar[2];   // accumulator read out (lives in the leader CTA)
     __shared__ uint64_t drain_bar;
@@ -169,8 +172,11 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&conv_bar[s], C::NUM_CONV_WARPS * CG);
             mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < SMALL_STAGES; ++s) {
+            mbar_init(&conv_bar[s], C::NUM_CONV_WARPS * CG);
+            mbar_init(&small_empty_bar[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full_bar[a], 1);
@@ -266,6 +272,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             const uint32_t idesc = make_idesc_tf32(C::UMMA_M, C::UMMA_N, args.a_mn_major, args.b_mn_major);
             int stage = 0;
             uint32_t phase = 0;
+            int sstage = 0;
+            uint32_t sphase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
@@ -283,9 +291,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             const uint32_t b_lbo = args.b_mn_major ? MN_BOX_BYTES : 16, b_sbo = args.b_mn_major ? 512 : 1024;
             const uint32_t b_kstep = args.b_mn_major ? 1024 : 32;
             const uint64_t b_swz = args.b_mn_major ? kSwizzle128Base32 : kSwizzle128;
-            uint32_t peer_empty[STAGES], peer_acc_full[2];
+            uint32_t peer_empty[STAGES], peer_small_empty[SMALL_STAGES], peer_acc_full[2];
             if constexpr (PAIR) {
                 for (int s = 0; s < STAGES; ++s) peer_empty[s] = mapa(smem_u32(&empty_bar[s]), 1);
+                for (int s = 0; s < SMALL_STAGES; ++s) peer_small_empty[s] = mapa(smem_u32(&small_empty_bar[s]), 1);
                 for (int a = 0; a < 2; ++a) peer_acc_full[a] = mapa(smem_u32(&acc_full_bar[a]), 1);
             }
             for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
@@ -300,7 +309,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     const int kb_begin = ch * k_chunk;
                     const int kb_end = (kb_begin + k_chunk < num_kb) ? kb_begin + k_chunk : num_kb;
                     for (int kb = kb_begin; kb < kb_end; ++kb) {
-                        if (!wait_or_abort<PAIR>(&conv_bar[stage], phase, abort_flag)) {
+                        if (!wait_or_abort<PAIR>(&conv_bar[sstage], sphase, abort_flag)) {
                             report(args.status, abort_flag, kErrMmaWait, static_cast<unsigned>(stage));
                             ok = false;
                             break;
@@ -308,8 +317,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                         tc_fence_after_sync();
                         const uint32_t a_raw = tiles_base + stage * STAGE_BYTES;
                         const uint32_t b_raw = a_raw + TILE_BYTES;
-                        const uint32_t a_small = a_raw + RAW_BYTES;
-                        const uint32_t b_small = b_raw + RAW_BYTES;
+                        const uint32_t a_small = tiles_base + SMALL_RING_OFFSET + sstage * STAGE_BYTES;
+                        const uint32_t b_small = a_small + TILE_BYTES;
 #pragma unroll
                         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                             const uint32_t fresh = (kb != kb_begin || kk != 0) ? 1u : 0u;
@@ -327,10 +336,18 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                             }
                         }
                         mma_commit<CG>(smem_u32(&empty_bar[stage]));
-                        if constexpr (PAIR) mma_commit<CG>(peer_empty[stage]);
+                        mma_commit<CG>(smem_u32(&small_empty_bar[sstage]));
+                        if constexpr (PAIR) {
+                            mma_commit<CG>(peer_empty[stage]);
+                            mma_commit<CG>(peer_small_empty[sstage]);
+                        }
                         if (++stage == STAGES) {
                             stage = 0;
                             phase ^= 1u;
+                        }
+                        if (++sstage == SMALL_STAGES) {
+                            sstage = 0;
+                            sphase ^= 1u;
                         }
                     }
                     if (!ok) break;
@@ -420,49 +437,70 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         constexpr int NCT = C::NUM_CONV_WARPS * 32;
         int stage = 0;
         uint32_t phase = 0;
+        int sstage = 0;
+        uint32_t sphase = 0;
         bool ok = true;
         const bool mask_big = args.mask_big != 0;
-        uint32_t conv_remote[STAGES] = {0, 0, 0};
+        uint32_t conv_remote[SMALL_STAGES] = {0, 0};
         if constexpr (PAIR) {
-            for (int s = 0; s < STAGES; ++s) conv_remote[s] = mapa(smem_u32(&conv_bar[s]), 0);
+            for (int s = 0; s < SMALL_STAGES; ++s) conv_remote[s] = mapa(smem_u32(&conv_bar[s]), 0);
         }
         for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
             for (int kb = 0; kb < num_kb; ++kb) {
-                if (!wait_or_abort<false>(&full_bar[stage], phase, abort_flag)) {
+                // The small slot must have been released by the MMAs that last read it, and the
+                // raw slot must have landed.
+                if (!wait_or_abort<PAIR>(&small_empty_bar[sstage], sphase ^ 1u, abort_flag) ||
+                    !wait_or_abort<false>(&full_bar[stage], phase, abort_flag)) {
                     if (lane == 0) report(args.status, abort_flag, kErrConverterWait, static_cast<unsigned>(stage));
                     ok = false;
                     break;
                 }
                 uint4 *raw = reinterpret_cast<uint4 *>(tiles + stage * STAGE_BYTES);
-                uint4 *small = reinterpret_cast<uint4 *>(tiles + stage * STAGE_BYTES + RAW_BYTES);
-#pragma unroll 4
-                for (int i = ctid; i < RAW_BYTES / 16; i += NCT) {
-                    const uint4 x = raw[i];
-                    uint4 big, sm;
-                    big.x = x.x & 0xFFFFE000u;
-                    big.y = x.y & 0xFFFFE000u;
-                    big.z = x.z & 0xFFFFE000u;
-                    big.w = x.w & 0xFFFFE000u;
-                    // small = x - big is exact; + 0x1000 on its bits rounds it to the nearest
-                    // TF32 value once the tensor core drops the low 13 bits.
-                    sm.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(big.x)) + 0x1000u;
-                    sm.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(big.y)) + 0x1000u;
-                    sm.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(big.z)) + 0x1000u;
-                    sm.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(big.w)) + 0x1000u;
-                    small[i] = sm;
-                    if (mask_big) raw[i] = big;
+                uint4 *small = reinterpret_cast<uint4 *>(tiles + SMALL_RING_OFFSET + sstage * STAGE_BYTES);
+                // All loads of a batch are issued before the first dependent instruction, so
+                // their shared-memory latencies overlap instead of adding up (a store to
+                // `small` could alias `raw` as far as the compiler knows, which would otherwise
+                // keep every load behind the previous store).
+                constexpr int PER_THREAD = RAW_BYTES / 16 / NCT;  // 16 x 16-byte words
+                constexpr int BATCH = 8;
+                static_assert(PER_THREAD % BATCH == 0, "converter batches must tile the stage");
+#pragma unroll
+                for (int base = 0; base < PER_THREAD; base += BATCH) {
+                    uint4 x[BATCH];
+#pragma unroll
+                    for (int u = 0; u < BATCH; ++u) x[u] = raw[ctid + (base + u) * NCT];
+#pragma unroll
+                    for (int u = 0; u < BATCH; ++u) {
+                        uint4 big, sm;
+                        big.x = x[u].x & 0xFFFFE000u;
+                        big.y = x[u].y & 0xFFFFE000u;
+                        big.z = x[u].z & 0xFFFFE000u;
+                        big.w = x[u].w & 0xFFFFE000u;
+                        // small = x - big is exact; + 0x1000 on its bits rounds it to the nearest
+                        // TF32 value once the tensor core drops the low 13 bits.
+                        sm.x = __float_as_uint(__uint_as_float(x[u].x) - __uint_as_float(big.x)) + 0x1000u;
+                        sm.y = __float_as_uint(__uint_as_float(x[u].y) - __uint_as_float(big.y)) + 0x1000u;
+                        sm.z = __float_as_uint(__uint_as_float(x[u].z) - __uint_as_float(big.z)) + 0x1000u;
+                        sm.w = __float_as_uint(__uint_as_float(x[u].w) - __uint_as_float(big.w)) + 0x1000u;
+                        small[ctid + (base + u) * NCT] = sm;
+                        if (mask_big) raw[ctid + (base + u) * NCT] = big;
+                    }
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     if constexpr (PAIR)
-                        mbar_arrive_cluster(conv_remote[stage]);
+                        mbar_arrive_cluster(conv_remote[sstage]);
                     else
-                        mbar_arrive(&conv_bar[stage]);
+                        mbar_arrive(&conv_bar[sstage]);
                 }
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
+                }
+                if (++sstage == SMALL_STAGES) {
+                    sstage = 0;
+                    sphase ^= 1u;
                 }
             }
         }

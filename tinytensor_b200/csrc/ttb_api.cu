@@ -29,7 +29,7 @@ struct Options {
     int tf32_terms = 3;
     int k_chunk = 0;
     int splitk = 1;
-    int two_cta = 0;
+    int two_cta = -1;  // -1 = choose by shape
     int mask_big = 0;
 };
 Options g_opt;
@@ -300,8 +300,14 @@ static int dispatch(const Problem &p) {
         // skinny outputs (a dim <= 16) are bandwidth-bound and go to the SIMT kernel.
         const bool big = p.N > 16 && p.M > 16 && p.K >= 16 &&
                          static_cast<double>(p.N) * p.M * p.K * p.B >= 128.0 * 128.0 * 64.0;
-        if (big && f32_tcgen05_eligible(p, why, sizeof(why)))
-            return launch_f32_tcgen05(p, f32_options(g_opt.two_cta != 0));
+        if (big && f32_tcgen05_eligible(p, why, sizeof(why))) {
+            // CTA pairs (256x256 tiles) halve shared-memory and L2 traffic per flop; they
+            // pay off once the output is more than one 128-wide tile in both dims and there
+            // are enough pair tiles to occupy a good part of the GPU.
+            const long long pair_tiles = ((p.N + 255) / 256) * ((p.M + 255) / 256) * p.B;
+            const bool pair = g_opt.two_cta < 0 ? (p.N > 128 && p.M > 128 && pair_tiles >= 24) : g_opt.two_cta != 0;
+            return launch_f32_tcgen05(p, f32_options(pair));
+        }
         return launch_simt(p, g_opt.splitk != 0);
     }
     if (p.dtype == TTB_F64) {
@@ -459,7 +465,11 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         return TTB_OK;
     }
     if (!strcmp(key, "two_cta")) {
-        g_opt.two_cta = value != 0;
+        if (value < -1 || value > 1) {
+            set_error("two_cta must be -1 (by shape), 0 or 1");
+            return TTB_EINVAL;
+        }
+        g_opt.two_cta = static_cast<int>(value);
         return TTB_OK;
     }
     if (!strcmp(key, "mask_big")) {
