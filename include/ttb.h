@@ -114,6 +114,37 @@ TTB_API int ttb_batched_matmul_strided_out(const ttb_view *lhs, const ttb_view *
 TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, void *out,
                                     int dtype, int device_id);
 
+/* The same product for callers that must not allocate device memory.
+ * Has no counterpart in the reference, whose runner allocates on every call
+ * (backend/cuda/matmul.cu:50).
+ *
+ * Some programs cannot let a library call cudaMalloc: they have given all
+ * device memory to an allocator of their own or run under a fixed memory
+ * budget, so an allocation from in here would fail or break that budget; or
+ * they sit in a latency-critical loop and cannot take the device-wide
+ * synchronisation that cudaMalloc and cudaFree bring.  The other entry points
+ * may grow a cached workspace when they split K; this one never allocates
+ * (no cudaMalloc, cudaFree or allocating library routine): it always runs the
+ * CUDA-core kernel with K split over thread blocks and keeps the partial sums
+ * in a 16 MiB array that is part of the library's device image (every GPU
+ * that loads the library holds those 16 MiB until the process exits).
+ *
+ * Limit: 2 * B * N * M * sizeof(element) must not exceed 16 MiB, otherwise
+ * TTB_ELIMIT with a message naming both sizes; nothing is launched then.
+ * All dtypes and all strides are accepted; `out` is contiguous [B,N,M].
+ *
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call before starting any stream
+ * capture.  All calls on a device share the one array: two calls whose
+ * kernels may overlap on the GPU (different streams, no ordering between
+ * them) race on it and give wrong results -- keep calls on one stream or
+ * order them with events.  The array keeps whatever the last call left in
+ * it; no clearing is needed, because a call overwrites every partial sum it
+ * later reads. */
+TTB_API int ttb_batched_matmul_static_scratch(const ttb_view *lhs, const ttb_view *rhs,
+                                              void *out, int dtype, int device_id,
+                                              void *stream);
+
 /* ---- multi-GPU partitioner (host logic only; no communication) ----------
  *
  * Splits lhs[B,N,K].rhs[B,K,M] over `world` GPUs the way the partitioner

@@ -15,6 +15,7 @@ from .backend import (  # noqa: F401
     Variant,
     batched_matmul,
     batched_matmul_host,
+    batched_matmul_static_scratch,
     check_device,
     get_option,
     last_variant,
@@ -29,7 +30,8 @@ from .backend import (  # noqa: F401
 from .partition import Partition, ShardedMatmul, partition  # noqa: F401
 
 __all__ = [
-    "TTBError", "Variant", "batched_matmul", "batched_matmul_host", "check_device", "get_option",
+    "TTBError", "Variant", "batched_matmul", "batched_matmul_host", "batched_matmul_static_scratch",
+    "check_device", "get_option",
     "last_variant", "launch_count", "lib", "lib_path", "matmul", "set_option", "tma_eligible",
     "view_of", "Partition", "ShardedMatmul", "partition",
 ]

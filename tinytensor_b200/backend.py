@@ -98,6 +98,9 @@ def lib() -> ctypes.CDLL:
         ctypes.c_void_p,
     ]
     L.ttb_batched_matmul_strided_out.restype = ctypes.c_int
+    L.ttb_batched_matmul_static_scratch.argtypes = [vp, vp, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                                    ctypes.c_void_p]
+    L.ttb_batched_matmul_static_scratch.restype = ctypes.c_int
     L.ttb_batched_matmul_host.argtypes = [vp, vp, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     L.ttb_batched_matmul_host.restype = ctypes.c_int
     L.ttb_partition.argtypes = [ctypes.c_int64] * 4 + [ctypes.c_int, ctypes.c_int, ctypes.c_int64,
@@ -223,6 +226,28 @@ def batched_matmul(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor | Non
         rc = L.ttb_batched_matmul_strided_out(
             ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.untyped_storage().data_ptr()),
             out.storage_offset(), strides, code, dev, ctypes.c_void_p(_stream_ptr(stream)))
+    if rc != 0:
+        _raise(rc)
+    return out
+
+
+def batched_matmul_static_scratch(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor, stream=None) -> torch.Tensor:
+    """The product through ``ttb_batched_matmul_static_scratch``: for callers that own all device
+    memory themselves (or cannot take cudaMalloc's device-wide synchronisation) the library
+    allocates nothing -- the caller passes `out` (contiguous [B,N,M]) and the K-split partial
+    sums live in a fixed 16 MiB device array.  Results above that limit raise TTBError.  Calls
+    that may overlap on the GPU race on the shared array; keep them on one stream."""
+    if lhs.dim() != 3 or rhs.dim() != 3 or lhs.dtype != rhs.dtype or lhs.device != rhs.device:
+        raise TTBError("operands must be rank-3 tensors of one dtype on one device")
+    if lhs.dtype not in _DTYPE_CODE:
+        raise TTBError(f"unsupported dtype {lhs.dtype}")
+    want = (lhs.shape[0], lhs.shape[1], rhs.shape[2])
+    if tuple(out.shape) != want or not out.is_contiguous() or out.dtype != lhs.dtype or out.device != lhs.device:
+        raise TTBError(f"out must be a contiguous {want} tensor of the operands' dtype and device")
+    dev = lhs.device.index if lhs.device.index is not None else torch.cuda.current_device()
+    lv, rv = view_of(lhs), view_of(rhs)
+    rc = lib().ttb_batched_matmul_static_scratch(ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.data_ptr()),
+                                                 _DTYPE_CODE[lhs.dtype], dev, ctypes.c_void_p(_stream_ptr(stream)))
     if rc != 0:
         _raise(rc)
     return out

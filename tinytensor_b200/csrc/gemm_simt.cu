@@ -17,6 +17,7 @@
 // vectors), double-buffered with register prefetch; each thread owns a
 // TM x TN register tile split in two halves per dim so that shared-memory reads
 // are conflict-free and global stores coalesce.
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -393,3 +394,129 @@ int launch_simt(const Problem &p, bool allow_splitk) {
 }
 
 }  // namespace ttb
+
+// ---------------------------------------------------------------------------
+// Split-K product with its scratch in a fixed device array (no allocation).
+//
+// Who needs this: a host program that has handed all device memory to an allocator of
+// its own (or runs under a hard memory budget), so that a cudaMalloc from inside this
+// library would fail or break the budget; and a latency-sensitive loop that cannot accept
+// the device-wide synchronisation cudaMalloc / cudaFree imply.  The ordinary entry points
+// grow a cached workspace with cudaMalloc when the K split needs one; this one never
+// allocates: the partial sums of the K split live in the array below, which every GPU
+// that loads the library holds from load until exit.
+namespace ttb {
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;  // 16 MiB, the documented limit
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address:
+// the address has to be asked for, per device, with that device current.
+constexpr int kStaticMaxDevices = 64;
+void *g_static_scratch_ptr[kStaticMaxDevices] = {nullptr};
+int g_static_sms[kStaticMaxDevices] = {0};
+std::mutex g_static_mu;
+
+int static_scratch_setup(int device, void **ptr, int *sms) {
+    if (device < 0 || device >= kStaticMaxDevices) {
+        set_error("device id %d out of range", device);
+        return TTB_EDEVICE;
+    }
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (g_static_scratch_ptr[device] == nullptr) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+        g_static_scratch_ptr[device] = p;
+        g_static_sms[device] = n;
+    }
+    *ptr = g_static_scratch_ptr[device];
+    *sms = g_static_sms[device];
+    return TTB_OK;
+}
+
+template <typename T>
+int launch_static_scratch_typed(const Problem &p, void *scratch, int sms) {
+    constexpr int BKs = sizeof(T) >= 8 ? 8 : 16;
+    const size_t per_split = static_cast<size_t>(p.B) * p.N * p.M * sizeof(T);
+    if (per_split == 0 || per_split * 2 > kStaticScratchBytes) {
+        set_error("result of %lld x %lld x %lld elements needs %zu bytes of scratch per K split; two splits do "
+                  "not fit the fixed %zu-byte scratch array of the no-allocation entry point",
+                  static_cast<long long>(p.B), static_cast<long long>(p.N), static_cast<long long>(p.M), per_split,
+                  kStaticScratchBytes);
+        return TTB_ELIMIT;
+    }
+    // Tile by output shape, as the ordinary SIMT dispatch does.
+    enum { MID, SKN, SKM, S } shape;
+    long long bm, bn;
+    if (p.M <= 16 && p.N > 16) {
+        shape = SKN; bm = 128; bn = 16;
+    } else if (p.N <= 16 && p.M > 16) {
+        shape = SKM; bm = 16; bn = 128;
+    } else if (p.N > 64 && p.M > 64) {
+        shape = MID; bm = 64; bn = 64;
+    } else {
+        shape = S; bm = 32; bn = 32;
+    }
+    const long long ntiles = ((p.N + bm - 1) / bm) * ((p.M + bn - 1) / bn) * p.B;
+    // As many K splits as fill the GPU twice over, at least two (this variant always goes
+    // through the scratch), each at least 8 K-blocks deep when K allows, and no more than
+    // the scratch array holds.
+    long long splits = (2LL * sms + ntiles - 1) / ntiles;
+    const long long by_k = p.K / (8LL * BKs);
+    if (splits > by_k) splits = by_k;
+    if (splits > 64) splits = 64;
+    const long long by_mem = static_cast<long long>(kStaticScratchBytes / per_split);
+    if (splits > by_mem) splits = by_mem;
+    if (splits < 2) splits = 2;
+    int rc;
+    switch (shape) {
+        case SKN: rc = launch_tile<T, 128, 16, BKs, 4, 2>(p, static_cast<int>(splits), scratch); break;
+        case SKM: rc = launch_tile<T, 16, 128, BKs, 2, 4>(p, static_cast<int>(splits), scratch); break;
+        case MID: rc = launch_tile<T, 64, 64, BKs, 4, 4>(p, static_cast<int>(splits), scratch); break;
+        default: rc = launch_tile<T, 32, 32, BKs, 2, 2>(p, static_cast<int>(splits), scratch); break;
+    }
+    if (rc == TTB_OK) note_launch(TTB_VARIANT_SIMT_SPLITK, 2);
+    return rc;
+}
+
+}  // namespace
+
+int resolve_problem(const ttb_view *lhs, const ttb_view *rhs, void *out, int dtype, int device, void *stream,
+                    Problem *p);
+
+}  // namespace ttb
+
+extern "C" TTB_API int ttb_batched_matmul_static_scratch(const ttb_view *lhs, const ttb_view *rhs, void *out,
+                                                         int dtype, int device_id, void *stream) {
+    using namespace ttb;
+    Problem p{};
+    int rc = resolve_problem(lhs, rhs, out, dtype, device_id, stream, &p);
+    if (rc != TTB_OK) return rc;
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceCount");
+    if (device_id < 0 || device_id >= ndev) {
+        set_error("device id %d out of range (have %d)", device_id, ndev);
+        return TTB_EDEVICE;
+    }
+    e = cudaSetDevice(device_id);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    void *scratch = nullptr;
+    int sms = 0;
+    rc = static_scratch_setup(device_id, &scratch, &sms);
+    if (rc != TTB_OK) return rc;
+    switch (p.dtype) {
+        case TTB_U8: return launch_static_scratch_typed<uint8_t>(p, scratch, sms);
+        case TTB_I16: return launch_static_scratch_typed<int16_t>(p, scratch, sms);
+        case TTB_I32: return launch_static_scratch_typed<int32_t>(p, scratch, sms);
+        case TTB_I64: return launch_static_scratch_typed<int64_t>(p, scratch, sms);
+        case TTB_F32: return launch_static_scratch_typed<float>(p, scratch, sms);
+        case TTB_F64: return launch_static_scratch_typed<double>(p, scratch, sms);
+        default: set_error("unsupported dtype %d", p.dtype); return TTB_EDTYPE;
+    }
+}

@@ -262,6 +262,12 @@ static F32Options f32_options(bool two_cta) {
     return o;
 }
 
+// Same checks and view resolution for entry points defined in other translation units.
+int resolve_problem(const ttb_view *lhs, const ttb_view *rhs, void *out, int dtype, int device, void *stream,
+                    Problem *p) {
+    return resolve(lhs, rhs, out, 0, nullptr, dtype, device, stream, p);
+}
+
 static int dispatch(const Problem &p) {
     DeviceState *d;
     int rc = device_state(p.device, &d);
