@@ -37,6 +37,9 @@ UNIT = "TFLOP/s"
 WORKLOAD = "C4: single 2D f32 GEMM 8192x8192x8192, N(0,1/sqrt(8192)) entries, seed 3"
 FLOPS_PER_STEP = 2.0 * DIM * DIM * DIM          # algorithmic: one multiply-add per (i, j, k)
 BYTES_PER_STEP = 3.0 * DIM * DIM * 4            # A and B read once, C written once
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the pair kernel on this very
+# workload, from one ncu capture (profiles/gemm_f32_3xtf32_pair_8192cubed.md): 2.304 GB + 0.257 GB.
+DRAM_TRAFFIC_PER_FULL_LAUNCH = 2.304e9 + 0.257e9
 
 
 def measured_peaks():
@@ -48,61 +51,80 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and clock-event (throttle) reasons through NVML in a thread
+    while the timed region runs.  Only reads; changes no setting."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {
+        "hw_slowdown": 0x8,            # nvmlClocksEventReasonHwSlowdown
+        "sw_thermal_slowdown": 0x20,   # nvmlClocksEventReasonSwThermalSlowdown
+        "hw_thermal_slowdown": 0x40,   # nvmlClocksThrottleReasonHwThermalSlowdown
+        "sw_power_cap": 0x4,           # nvmlClocksEventReasonSwPowerCap
+    }
 
-    def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
-        self.proc = None
-        self.lines = []
+    def __init__(self, torch_device_index: int):
+        self.samples = []
+        self.stop_flag = threading.Event()
+        self.thread = None
+        self.handle = None
+        self.nvml = None
+        try:
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            try:
+                uuid = str(torch.cuda.get_device_properties(torch_device_index).uuid)
+                if not uuid.startswith("GPU-"):
+                    uuid = "GPU-" + uuid
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(torch_device_index)
+        except Exception:
+            self.nvml = None
+
+    def _loop(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                power = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                try:
+                    reasons = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    reasons = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.samples.append((time.perf_counter(), sm, power, reasons))
+            except Exception:
+                pass
+            time.sleep(0.01)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+        if self.nvml is None:
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+    def stop(self, t_begin=None, t_end=None):
+        if self.nvml is None or self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["NVML unavailable"]}
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        n = self.nvml
         try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
-                power.append(float(f[3]))
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # "under load": the upper half of the samples by power draw
-        order = np.argsort(power)
-        load = [sm[i] for i in order[len(order) // 2:]]
-        return {"sm_mhz": float(np.median(load)), "sm_max_mhz": float(max(smax)), "power_w_max": float(max(power)),
-                "samples": len(sm), "reasons": sorted(reasons)}
+            sm_max = float(n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM))
+        except Exception:
+            sm_max = None
+        sel = [x for x in self.samples if (t_begin is None or x[0] >= t_begin) and (t_end is None or x[0] <= t_end)]
+        if not sel:
+            sel = self.samples
+        if not sel:
+            return {"sm_mhz": None, "sm_max_mhz": sm_max, "reasons": ["no samples"]}
+        bits = 0
+        for x in sel:
+            bits |= int(x[3])
+        reasons = sorted(name for name, mask in self.REASONS.items() if bits & mask)
+        return {"sm_mhz": float(np.median([x[1] for x in sel])), "sm_max_mhz": sm_max,
+                "power_w_max": float(max(x[2] for x in sel)), "samples": len(sel), "reasons": reasons}
 
 
 # --------------------------------------------------------------------------- reference arm
@@ -224,14 +246,16 @@ def run_ours(args):
     launches0 = ttb.launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_begin = time.perf_counter()
     start.record()
     for _ in range(args.steps):
         step()
     stop.record()
     barrier()
+    t_end = time.perf_counter()
     elapsed_ms = start.elapsed_time(stop)
     launches = ttb.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
 
     # kernel-only timing for the roofline (same stream, events around the launches)
     for _ in range(2):
@@ -304,19 +328,13 @@ def run_ours(args):
                     "api": "ttb_batched_matmul_host (pinned host buffers, copies inside the timed region)"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                         "traffic": None, "kernel_ms": kernel_ms,
+                         "traffic": DRAM_TRAFFIC_PER_FULL_LAUNCH * share, "kernel_ms": kernel_ms,
                          "peak_source": f"{peak_kind}: bf16 sustained {bf16} TFLOP/s / 2 (TF32) / 3 (passes)",
                          "tf32_pipe_tflops": 3.0 * achieved, "hbm_gbs_algorithmic": BYTES_PER_STEP * share / (kernel_ms * 1e-3) / 1e9},
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": kind,
                              "sample": f"first {rows} of {DIM} lhs rows (1/{DIM // rows} of the product), {cpu_s:.1f} s",
                              "host_cores_available": os.cpu_count()},
         }
-        traffic_file = ROOT / "profiles" / "traffic.json"
-        if traffic_file.exists():
-            try:
-                line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get("gemm_f32_8192_dram_bytes_per_launch")
-            except (ValueError, OSError):
-                pass
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -104,6 +104,24 @@ TTB_API int ttb_batched_matmul_strided_out(const ttb_view *lhs, const ttb_view *
                                            const int64_t out_stride[3], int dtype,
                                            int device_id, void *stream);
 
+/* Product fused with an all-gather of the result over NVLink (f32, tensor-core
+ * kernel only).  Computes lhs . rhs into the strided destination `out` on this GPU
+ * like ttb_batched_matmul_strided_out, and stores every finished tile into the
+ * same place (same out_offset, same strides) of each of the `n_peers` buffers
+ * peer_out[i]: device pointers to the other GPUs' C that are mapped into this
+ * process (peer access, symmetric memory, IPC).  The peer stores are plain
+ * st.global issued by dedicated warps of the GEMM kernel, so the exchange
+ * overlaps the math tile by tile.  When the kernel has completed on every
+ * rank, and the ranks have then synchronised with each other (the caller's
+ * job: e.g. a symmetric-memory or NCCL barrier on the same stream), every
+ * rank holds the complete C.  n_peers == 0 degenerates to the plain product.
+ * No counterpart in the reference (single-device matmul, host-bounce copies
+ * between devices, autograd/unary_ops.cpp:67-83). */
+TTB_API int ttb_matmul_allgather(const ttb_view *lhs, const ttb_view *rhs, void *out,
+                                 int64_t out_offset, const int64_t out_stride[3],
+                                 void *const *peer_out, int n_peers, int dtype,
+                                 int device_id, void *stream);
+
 /* Host-buffer form: lhs/rhs `data` and `out` are HOST pointers (pinned memory
  * makes the copies asynchronous).  Copies the operands' storage spans to the
  * device, runs ttb_batched_matmul on `device_id`, copies the contiguous result

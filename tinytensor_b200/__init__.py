@@ -23,6 +23,7 @@ from .backend import (  # noqa: F401
     lib,
     lib_path,
     matmul,
+    matmul_allgather,
     set_option,
     tma_eligible,
     view_of,
@@ -32,6 +33,6 @@ from .partition import Partition, ShardedMatmul, partition  # noqa: F401
 __all__ = [
     "TTBError", "Variant", "batched_matmul", "batched_matmul_host", "batched_matmul_static_scratch",
     "check_device", "get_option",
-    "last_variant", "launch_count", "lib", "lib_path", "matmul", "set_option", "tma_eligible",
+    "last_variant", "launch_count", "lib", "lib_path", "matmul", "matmul_allgather", "set_option", "tma_eligible",
     "view_of", "Partition", "ShardedMatmul", "partition",
 ]

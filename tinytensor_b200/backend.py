@@ -98,6 +98,10 @@ def lib() -> ctypes.CDLL:
         ctypes.c_void_p,
     ]
     L.ttb_batched_matmul_strided_out.restype = ctypes.c_int
+    L.ttb_matmul_allgather.argtypes = [
+        vp, vp, ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_void_p),
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    L.ttb_matmul_allgather.restype = ctypes.c_int
     L.ttb_batched_matmul_static_scratch.argtypes = [vp, vp, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                                     ctypes.c_void_p]
     L.ttb_batched_matmul_static_scratch.restype = ctypes.c_int
@@ -226,6 +230,29 @@ def batched_matmul(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor | Non
         rc = L.ttb_batched_matmul_strided_out(
             ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.untyped_storage().data_ptr()),
             out.storage_offset(), strides, code, dev, ctypes.c_void_p(_stream_ptr(stream)))
+    if rc != 0:
+        _raise(rc)
+    return out
+
+
+def matmul_allgather(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor, peer_bases, stream=None) -> torch.Tensor:
+    """``ttb_matmul_allgather``: lhs . rhs into `out` (a rank-3, possibly strided view of this
+    rank's full C) and, tile by tile from inside the GEMM kernel, into the same place of every
+    peer's C.  `peer_bases` are device pointers to the START of the peers' C storages, mapped
+    into this process (e.g. ``symmetric_memory`` buffer pointers); the peers' buffers must be laid
+    out like this rank's.  f32 on the tensor-core kernel only.  The caller synchronises the
+    ranks afterwards."""
+    if lhs.dtype != torch.float32 or rhs.dtype != torch.float32 or out.dtype != torch.float32:
+        raise TTBError("matmul_allgather: f32 only")
+    if out.dim() != 3 or tuple(out.shape) != (lhs.shape[0], lhs.shape[1], rhs.shape[2]):
+        raise TTBError("matmul_allgather: out has the wrong shape")
+    dev = lhs.device.index if lhs.device.index is not None else torch.cuda.current_device()
+    lv, rv = view_of(lhs), view_of(rhs)
+    strides = (ctypes.c_int64 * 3)(*out.stride())
+    peers = (ctypes.c_void_p * max(len(peer_bases), 1))(*[ctypes.c_void_p(int(p)) for p in peer_bases])
+    rc = lib().ttb_matmul_allgather(ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.untyped_storage().data_ptr()),
+                                out.storage_offset(), strides, peers, len(peer_bases), _DTYPE_CODE[lhs.dtype], dev,
+                                ctypes.c_void_p(_stream_ptr(stream)))
     if rc != 0:
         _raise(rc)
     return out

@@ -38,7 +38,8 @@ enum DeviceErrorCode : unsigned int {
     kErrConverterWait = 2,
     kErrMmaWait = 3,
     kErrEpilogueWait = 4,
-    kErrAccEmptyWait = 5
+    kErrAccEmptyWait = 5,
+    kErrForwardWait = 6
 };
 
 void set_error(const char *fmt, ...);
@@ -57,7 +58,9 @@ struct F32Options {
     int two_cta = 0;    // use CTA pairs (cta_group::2)
     int mask_big = 0;   // converters also rewrite the raw tile with its masked big part (test only)
 };
-int launch_f32_tcgen05(const Problem &p, const F32Options &opt);
+// n_peers > 0 fuses an all-gather into the product: every finished tile is also stored into
+// peer_c[i] (peer-mapped pointers to the other GPUs' C, same layout as p.c).
+int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers = 0, void *const *peer_c = nullptr);
 bool f32_tcgen05_eligible(const Problem &p, char *why, int why_len);
 int launch_f64_dmma(const Problem &p);
 bool f64_dmma_eligible(const Problem &p);

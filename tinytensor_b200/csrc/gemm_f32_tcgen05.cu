@@ -63,6 +63,7 @@ constexpr int SMALL_RING_OFFSET = STAGES * STAGE_BYTES;
 constexpr int SMEM_BYTES = (STAGES + SMALL_STAGES) * STAGE_BYTES + 1024;  // + alignment slack
 constexpr int MN_BOX_BYTES = 32 * BK * 4;      // one MN-major TMA box: 32 (MN) x BK (K)
 constexpr int DEFAULT_K_CHUNK = 8;             // K blocks summed inside TMEM
+constexpr int kMaxPeers = 15;                  // fused all-gather: peers besides this GPU
 
 template <int CG>
 struct Cfg {
@@ -92,6 +93,8 @@ struct alignas(64) TcArgs {
     int terms;     // 3 = split-TF32, 1 = single pass (test only)
     int k_chunk;   // K blocks per TMEM accumulation chunk
     int mask_big;  // converters also overwrite the raw tile with its masked big part
+    int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
+    float *peer_c[kMaxPeers];  // their C, laid out exactly like `c` (same offset and strides)
     DeviceStatus *status;
 };
 
@@ -153,6 +156,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     __shared__ uint64_t small_empty_bar[SMALL_STAGES];  // MMAs that read the small slot are done (local)
     __shared__ uint64_t acc_full_bar[2];    // accumulator chunk complete (local)
     __shared__ uint64_t acc_empty_bar[2];   // accumulator read out (lives in the leader CTA)
+    __shared__ uint64_t out_full_bar[2];    // tile stored into this GPU's C (epilogue -> forwarding warps)
+    __shared__ uint64_t out_empty_bar[2];   // tile forwarded to every peer (forwarding warps -> epilogue)
     __shared__ uint64_t drain_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
@@ -181,6 +186,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full_bar[a], 1);
             mbar_init(&acc_empty_bar[a], 4 * C::EPI_WGS * CG);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&out_full_bar[a], 4 * C::EPI_WGS);
+            mbar_init(&out_empty_bar[a], 2);
         }
         mbar_init(&drain_bar, 1);
         abort_flag_s = 0;
@@ -362,6 +371,86 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             for (int i = 0; i < 1000000; ++i)
                 if (mbar_try_wait(&drain_bar, 0)) break;
         }
+      } else if (args.n_peers > 0) {
+        // ------------------------------------------------------------ forwarding (warps 2-3)
+        // All-gather fused into the product: once the epilogue has stored a tile into this
+        // GPU's C, these two warps read it back (it is still in L2) and store it into the same
+        // place of every peer GPU's C through peer-mapped pointers (plain st.global over
+        // NVLink).  They are the only threads that NVLink back-pressure can stall; the MMA,
+        // converter and epilogue warps keep going, so the exchange overlaps the math tile by
+        // tile.  The two-slot full/empty handshake keeps the epilogue at most two tiles ahead.
+        const int stid = threadIdx.x - 64;                    // 0..63
+        constexpr int ROW_VEC = C::TILE_N / 4;                // float4 per tile row
+        constexpr int TOTAL_VEC = BM * ROW_VEC;               // this CTA's 128 rows
+        constexpr int FWD_BATCH = 8;
+        const bool vec_ok = args.c_sj == 1 && (args.c_si & 3) == 0 && (args.c_sb & 3) == 0 &&
+                            (reinterpret_cast<uintptr_t>(args.c) & 15) == 0;
+        int oslot = 0;
+        uint32_t ophase = 0;
+        bool ok = true;
+        for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
+            int b, tm, tn;
+            tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
+            if (!wait_or_abort<false>(&out_full_bar[oslot], ophase, abort_flag)) {
+                if (lane == 0) report(args.status, abort_flag, kErrForwardWait, 16u + static_cast<unsigned>(oslot));
+                ok = false;
+                break;
+            }
+            const int row0 = tm * C::TILE_M + static_cast<int>(cta_rank) * BM;
+            const int col0 = tn * C::TILE_N;
+            const long long base = static_cast<long long>(b) * args.c_sb;
+            if (vec_ok) {
+                for (int it = 0; it < TOTAL_VEC / 64; it += FWD_BATCH) {
+                    float4 v[FWD_BATCH];
+                    unsigned valid = 0;
+#pragma unroll
+                    for (int u = 0; u < FWD_BATCH; ++u) {
+                        const int idx = stid + (it + u) * 64;
+                        const int r = row0 + idx / ROW_VEC;
+                        const int cc = col0 + (idx % ROW_VEC) * 4;
+                        // whole vectors only; a ragged right edge is handled below
+                        if (r < args.N && cc + 4 <= args.M) {
+                            valid |= 1u << u;
+                            v[u] = __ldcg(reinterpret_cast<const float4 *>(
+                                args.c + base + static_cast<long long>(r) * args.c_si + cc));
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < FWD_BATCH; ++u) {
+                        if (valid & (1u << u)) {
+                            const int idx = stid + (it + u) * 64;
+                            const long long o = base + static_cast<long long>(row0 + idx / ROW_VEC) * args.c_si +
+                                                col0 + (idx % ROW_VEC) * 4;
+                            for (int pr = 0; pr < args.n_peers; ++pr)
+                                *reinterpret_cast<float4 *>(args.peer_c[pr] + o) = v[u];
+                        }
+                    }
+                }
+            }
+            // Scalar path: everything when the destination is not vector-aligned, else only
+            // the columns of a ragged right edge.
+            if (!vec_ok || (args.M & 3) != 0) {
+                const int edge_begin = vec_ok ? (args.M - (args.M & 3)) : 0;
+                for (int idx = stid; idx < BM * C::TILE_N; idx += 64) {
+                    const int r = row0 + idx / C::TILE_N;
+                    const int cc = col0 + idx % C::TILE_N;
+                    if (r < args.N && cc < args.M && cc >= edge_begin) {
+                        const long long o = base + static_cast<long long>(r) * args.c_si +
+                                            static_cast<long long>(cc) * args.c_sj;
+                        const float x = __ldcg(args.c + o);
+                        for (int pr = 0; pr < args.n_peers; ++pr) args.peer_c[pr][o] = x;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&out_empty_bar[oslot]);
+            if (++oslot == 2) {
+                oslot = 0;
+                ophase ^= 1u;
+            }
+        }
+        // Peer stores must have left this GPU before the kernel is reported complete.
+        __threadfence_system();
       }
     } else if (warp < C::FIRST_CONV_WARP) {
         // ------------------------------------------------------------ epilogue
@@ -378,6 +467,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             for (int a = 0; a < 2; ++a) acc_empty_remote[a] = mapa(smem_u32(&acc_empty_bar[a]), 0);
         }
         float sum[128];
+        int oslot = 0;
+        uint32_t ophase = 0;
         for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
             int b, tm, tn;
             tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
@@ -416,6 +507,14 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             if (!ok) break;
             const int row = tm * C::TILE_M + static_cast<int>(cta_rank) * BM + quarter * 32 + lane;
             const int col0 = tn * C::TILE_N + col_half * 128;
+            if (args.n_peers > 0) {
+                // The forwarding warps must be done with the tile that last used this slot.
+                if (!wait_or_abort<false>(&out_empty_bar[oslot], ophase ^ 1u, abort_flag)) {
+                    if (lane == 0) report(args.status, abort_flag, kErrForwardWait, static_cast<unsigned>(oslot));
+                    ok = false;
+                    break;
+                }
+            }
             if (row < args.N && col0 < args.M) {
                 float *crow = args.c + static_cast<long long>(b) * args.c_sb + static_cast<long long>(row) * args.c_si;
                 if (vec_ok && col0 + 128 <= args.M) {
@@ -427,6 +526,16 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 #pragma unroll
                     for (int j = 0; j < 128; ++j)
                         if (col0 + j < args.M) crow[static_cast<long long>(col0 + j) * args.c_sj] = sum[j];
+                }
+            }
+            if (args.n_peers > 0) {
+                // Publish the tile (now in this GPU's C) to the forwarding warps.
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&out_full_bar[oslot]);
+                if (++oslot == 2) {
+                    oslot = 0;
+                    ophase ^= 1u;
                 }
             }
         }
@@ -608,7 +717,7 @@ bool f32_tcgen05_eligible(const Problem &p, char *why, int why_len) {
     return plan(p, &pl, why, why_len);
 }
 
-int launch_f32_tcgen05(const Problem &p, const F32Options &opt) {
+int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, void *const *peer_c) {
     TcPlan pl;
     char why[200] = "";
     if (!plan(p, &pl, why, sizeof(why))) {
@@ -638,6 +747,12 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt) {
     args.k_chunk = opt.k_chunk > 0 ? opt.k_chunk : DEFAULT_K_CHUNK;
     if (opt.k_chunk < 0) args.k_chunk = 0;  // whole K inside TMEM (test only)
     args.mask_big = opt.mask_big;
+    if (n_peers < 0 || n_peers > kMaxPeers) {
+        set_error("fused all-gather takes at most %d peers, got %d", kMaxPeers, n_peers);
+        return TTB_ELIMIT;
+    }
+    args.n_peers = n_peers;
+    for (int i = 0; i < n_peers; ++i) args.peer_c[i] = static_cast<float *>(peer_c[i]);
     int rc = device_status_ptr(p.device, &args.status);
     if (rc != TTB_OK) return rc;
     int sms = 148;

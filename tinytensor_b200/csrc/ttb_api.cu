@@ -350,6 +350,45 @@ TTB_API int ttb_batched_matmul_strided_out(const ttb_view *lhs, const ttb_view *
     return dispatch(p);
 }
 
+TTB_API int ttb_matmul_allgather(const ttb_view *lhs, const ttb_view *rhs, void *out, int64_t out_offset,
+                                 const int64_t out_stride[3], void *const *peer_out, int n_peers, int dtype,
+                                 int device_id, void *stream) {
+    if (!out_stride || n_peers < 0 || (n_peers > 0 && !peer_out)) {
+        set_error("ttb_matmul_allgather: null out_stride / peer_out or negative n_peers");
+        return TTB_EINVAL;
+    }
+    Problem p{};
+    int rc = resolve(lhs, rhs, out, out_offset, out_stride, dtype, device_id, stream, &p);
+    if (rc != TTB_OK) return rc;
+    if (n_peers == 0) return dispatch(p);
+    char why[160] = "";
+    if (p.dtype != TTB_F32 || !f32_tcgen05_eligible(p, why, sizeof(why))) {
+        set_error("ttb_matmul_allgather: the fused exchange exists for the f32 tensor-core kernel only (%s)",
+                  p.dtype != TTB_F32 ? "dtype is not f32" : why);
+        return TTB_EUNSUPPORTED;
+    }
+    DeviceState *d;
+    rc = device_state(p.device, &d);
+    if (rc != TTB_OK) return rc;
+    cudaError_t e = cudaSetDevice(p.device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    void *peers[16];
+    if (n_peers > 15) {
+        set_error("ttb_matmul_allgather: at most 15 peers, got %d", n_peers);
+        return TTB_ELIMIT;
+    }
+    for (int i = 0; i < n_peers; ++i) {
+        if (!peer_out[i]) {
+            set_error("ttb_matmul_allgather: peer_out[%d] is null", i);
+            return TTB_EINVAL;
+        }
+        peers[i] = static_cast<char *>(peer_out[i]) + out_offset * 4;
+    }
+    const long long pair_tiles = ((p.N + 255) / 256) * ((p.M + 255) / 256) * p.B;
+    const bool pair = g_opt.two_cta < 0 ? (p.N > 128 && p.M > 128 && pair_tiles >= 24) : g_opt.two_cta != 0;
+    return launch_f32_tcgen05(p, f32_options(pair), n_peers, peers);
+}
+
 TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, void *out, int dtype,
                                     int device_id) {
     Problem p{};

@@ -72,6 +72,31 @@ class ShardedMatmul:
         self._local = local_matmul or (lambda a, b, o: backend.batched_matmul(a, b, out=o))
         self._stage: Optional[torch.Tensor] = None
         self._gathered: Optional[torch.Tensor] = None
+        self._symm = None  # (tensor, symmetric-memory handle) of the fused path's C
+
+    # -- fused exchange: C lives in symmetric memory so that every rank can store into every C
+    def symmetric_output(self, shape, dtype: torch.dtype, device) -> torch.Tensor:
+        """Allocates this rank's C in ``torch.distributed`` symmetric memory and exchanges the
+        peer mappings (a collective: every rank must call it with the same shape).  A product
+        whose `out` is this tensor uses the fused GEMM + all-gather kernel: the column block is
+        computed into it and stored, tile by tile from inside the kernel, into the peers' C
+        over NVLink; one symmetric-memory barrier per product replaces the NCCL all-gather and
+        the re-layout pass."""
+        import torch.distributed._symmetric_memory as symm
+
+        t = symm.empty(tuple(shape), dtype=dtype, device=device)
+        group = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm.rendezvous(t, group.group_name)
+        if int(hdl.buffer_ptrs[hdl.rank]) != t.untyped_storage().data_ptr():
+            raise backend.TTBError("symmetric buffer does not start at the tensor's storage")
+        self._symm = (t, hdl)
+        return t
+
+    def _fused_ok(self, lhs: torch.Tensor, out: Optional[torch.Tensor]) -> bool:
+        if self._symm is None or out is None or lhs.dtype != torch.float32:
+            return False
+        t, _ = self._symm
+        return out.untyped_storage().data_ptr() == t.untyped_storage().data_ptr()
 
     def plan(self, lhs: torch.Tensor, rhs: torch.Tensor) -> Partition:
         B, N, K = lhs.shape
@@ -131,6 +156,14 @@ class ShardedMatmul:
         if self.world == 1 or not gather:
             if part.size > 0:
                 self._local(lhs, rhs[:, :, part.begin:part.end], out[:, :, part.begin:part.end])
+            return out
+        if self._fused_ok(lhs, out):
+            # One kernel computes the block and pushes it to every peer; then the ranks meet.
+            _, hdl = self._symm
+            peers = [int(hdl.buffer_ptrs[r]) for r in range(self.world) if r != self.rank]
+            if part.size > 0:
+                backend.matmul_allgather(lhs, rhs[:, :, part.begin:part.end], out[:, :, part.begin:part.end], peers)
+            hdl.barrier()
             return out
         parts = [partition(1, N, lhs.shape[2], M, self.world, r, self.col_align) for r in range(self.world)]
         width = max(p.size for p in parts)
