@@ -217,8 +217,13 @@ def run_ours(args):
     std = DIM ** -0.5
     A = torch.randn((1, DIM, DIM), generator=g, device=dev) * std
     B = torch.randn((1, DIM, DIM), generator=g, device=dev) * std
-    C = torch.empty((1, DIM, DIM), device=dev)
     sharded = ttb.ShardedMatmul() if world > 1 else None
+    if world > 1 and args.exchange == "fused":
+        # C in symmetric memory: the GEMM kernel itself stores each finished tile into every
+        # rank's C over NVLink (fused all-gather); "nccl" keeps C private and all-gathers after.
+        C = sharded.symmetric_output((1, DIM, DIM), torch.float32, dev)
+    else:
+        C = torch.empty((1, DIM, DIM), device=dev)
     part = ttb.partition(1, DIM, DIM, DIM, world, rank)
 
     def step():
@@ -315,11 +320,46 @@ def run_ours(args):
         a_rows, b_host = host_operands(rows)
         cpu_s = cpu_sample_seconds(lib, kind, a_rows, b_host)
         cpu_value = 2.0 * rows * DIM * DIM / cpu_s / 1e12
+        # The kernel this library replaces, as a second reported baseline (N = 1 only): the
+        # reference's own CUDA matmul kernel compiled from its sources (oracle/_ref), run on
+        # this GPU on the same operands through the launch configuration of its runner.
+        existing = None
+        ref_cuda_path = ROOT / "oracle" / "_ref" / "libttref_cuda.so"
+        if world == 1 and ref_cuda_path.exists():
+            rc_lib = ctypes.CDLL(str(ref_cuda_path))
+            rc_lib.ref_cuda_matmul_f32.restype = ctypes.c_int
+            Cref = torch.empty((1, DIM, DIM), device=dev)
+
+            def ref_kernel():
+                rc = rc_lib.ref_cuda_matmul_f32(
+                    ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(B.data_ptr()), ctypes.c_void_p(Cref.data_ptr()),
+                    ctypes.c_int(1), ctypes.c_int(DIM), ctypes.c_int(DIM), ctypes.c_int(DIM),
+                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                if rc != 0:
+                    raise RuntimeError(f"reference CUDA kernel launch failed: cudaError {rc}")
+
+            ref_kernel()
+            torch.cuda.synchronize()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record()
+            for _ in range(2):
+                ref_kernel()
+            r1.record()
+            torch.cuda.synchronize()
+            ref_ms = r0.elapsed_time(r1) / 2
+            diff = float((Cref[0, :64] - C[0, :64]).abs().max() / C[0, :64].abs().max())
+            existing = {"value": FLOPS_PER_STEP / (ref_ms * 1e-3) / 1e12, "unit": UNIT, "ms": ref_ms,
+                        "kind": "reference",
+                        "what": "tinytensor's matmul_kernel<float> (backend/cuda/kernel/matmul.cuh) compiled for sm_100a",
+                        "max_diff_vs_ours_rel_to_max": diff}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": f"column blocks x{world} + all-gather of C" if world > 1 else "single GPU",
+            "config": {"workload": WORKLOAD,
+                       "parallelism": (f"column blocks x{world} + all-gather of C "
+                                       f"({'fused into the GEMM kernel, peer stores over NVLink' if args.exchange == 'fused' else 'NCCL all_gather + re-layout'})")
+                       if world > 1 else "single GPU",
                        "l2": "operands (768 MiB with C) exceed the 126 MB L2; no explicit flush",
                        "kernel": variant, "arithmetic": "3xTF32 split on tcgen05, fp32 accumulate"},
             "clocks": clocks,
@@ -334,6 +374,7 @@ def run_ours(args):
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": kind,
                              "sample": f"first {rows} of {DIM} lhs rows (1/{DIM // rows} of the product), {cpu_s:.1f} s",
                              "host_cores_available": os.cpu_count()},
+            "existing_gpu_kernel": existing,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -346,6 +387,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: how C is all-gathered (fused into the GEMM kernel, or NCCL after it)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

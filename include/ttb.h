@@ -190,7 +190,8 @@ TTB_API const char *ttb_variant_name(int variant);
  * partial sum is folded into fp32 registers; 0 = default of 8, -1 = whole K,
  * test only), "two_cta" (automatic dispatch: -1 = pick the CTA-pair kernel by
  * shape, default; 0 = never; 1 = always),
- * "splitk" (0 = never split K in the SIMT kernel), "mask_big" (test only).
+ * "splitk" (0 = never split K in the SIMT kernel), "mask_big" (test only),
+ * "tc_profile" (1 = record wait-cycle counters, see ttb_tc_profile).
  * Returns TTB_EINVAL for an unknown key or value. */
 TTB_API int ttb_set_option(const char *key, int64_t value);
 TTB_API int64_t ttb_get_option(const char *key);
@@ -200,6 +201,16 @@ TTB_API int ttb_device_count(void);
  * bounded wait inside a kernel gave up).  Synchronises the device.
  * Returns TTB_OK, TTB_ETIMEOUT, or another negative status. */
 TTB_API int ttb_check_device(int device_id);
+/* Tracing aid for the f32 tensor-core kernel.  With the "tc_profile" option
+ * set to 1, every CTA of that kernel records eight cycle counters: time its
+ * TMA producer waited for a free shared-memory slot, its MMA thread for a
+ * free accumulator and for converted tiles, its first converter thread for a
+ * free small-tile slot, for TMA data, and spent converting, its first epilogue
+ * warp for a finished accumulator, and the CTA's lifetime.  Copies the
+ * counters of the first `ctas` CTAs (8 values each) of the last such launch
+ * into `out`; synchronises the device.  The reference has no tracing at all
+ * (only a Graphviz dump of the autograd graph, tensor.cpp:3225). */
+TTB_API int ttb_tc_profile(int device_id, int64_t *out, int ctas);
 /* 1 if this view can be fed to the tensor-core kernels through a TMA
  * descriptor (16-byte aligned base, unit stride on one matrix dim, other
  * byte strides multiples of 16), else 0; `operand` 0 = lhs, 1 = rhs.

@@ -70,6 +70,37 @@ class Oracle:
         return out
 
 
+class RefCuda:
+    """The reference's own CUDA matmul kernel (oracle/_ref/libttref_cuda.so), launched the way
+    its runner launches it: contiguous operands, default stream."""
+
+    def __init__(self, lib: ctypes.CDLL):
+        self.lib = lib
+
+    def matmul(self, lhs, rhs):
+        import torch
+
+        names = {torch.uint8: "u8", torch.int16: "i16", torch.int32: "i32", torch.int64: "i64",
+                 torch.float32: "f32", torch.float64: "f64"}
+        lhs, rhs = lhs.contiguous(), rhs.contiguous()  # backend/cuda/matmul.cu:40-41
+        B, N, K = lhs.shape
+        M = rhs.shape[2]
+        out = torch.empty((B, N, M), dtype=lhs.dtype, device=lhs.device)
+        fn = getattr(self.lib, f"ref_cuda_matmul_{names[lhs.dtype]}")
+        fn.restype = ctypes.c_int
+        rc = fn(ctypes.c_void_p(lhs.data_ptr()), ctypes.c_void_p(rhs.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                ctypes.c_int(B), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(M),
+                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0, f"reference CUDA kernel launch failed: cudaError {rc}"
+        return out
+
+
+def load_ref_cuda():
+    """None when the library was not built (no reference tree at build time)."""
+    path = ORACLE_DIR / "_ref" / "libttref_cuda.so"
+    return RefCuda(ctypes.CDLL(str(path))) if path.exists() else None
+
+
 def load() -> Oracle:
     port = ORACLE_DIR / "liboracle.so"
     if not port.exists():

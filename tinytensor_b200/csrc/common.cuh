@@ -49,6 +49,9 @@ void note_launch(int variant, int count);
 // Returns the device-resident status word of `device` (allocated on first use).
 int device_status_ptr(int device, DeviceStatus **out);
 int sm_count(int device, int *out);
+// Device buffer for the tcgen05 kernel's wait-cycle counters, or nullptr when the
+// "tc_profile" option is off.
+long long *profile_ptr(int device);
 
 // Per-dtype launchers.  Each returns a ttb_status.
 int launch_simt(const Problem &p, bool allow_splitk);
@@ -57,6 +60,7 @@ struct F32Options {
     int k_chunk = 0;    // K blocks accumulated in TMEM before folding into registers (0 = all)
     int two_cta = 0;    // use CTA pairs (cta_group::2)
     int mask_big = 0;   // converters also rewrite the raw tile with its masked big part (test only)
+    int dbg = 0;        // timing experiments (wrong results when non-zero)
 };
 // n_peers > 0 fuses an all-gather into the product: every finished tile is also stored into
 // peer_c[i] (peer-mapped pointers to the other GPUs' C, same layout as p.c).

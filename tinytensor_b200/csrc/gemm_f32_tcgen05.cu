@@ -64,6 +64,11 @@ constexpr int SMEM_BYTES = (STAGES + SMALL_STAGES) * STAGE_BYTES + 1024;  // + a
 constexpr int MN_BOX_BYTES = 32 * BK * 4;      // one MN-major TMA box: 32 (MN) x BK (K)
 constexpr int DEFAULT_K_CHUNK = 8;             // K blocks summed inside TMEM
 constexpr int kMaxPeers = 15;                  // fused all-gather: peers besides this GPU
+// Profile slots per CTA: cycles the producer waited for a free raw slot, the MMA thread for a
+// free accumulator / for converted tiles, converter thread 0 for a free small slot / for TMA data /
+// spent converting, the first epilogue warp for a full accumulator, and the CTA's lifetime.
+enum { kProfProducerEmpty = 0, kProfMmaAccEmpty, kProfMmaConv, kProfConvSmallEmpty, kProfConvFull, kProfConvBusy,
+       kProfEpiAccFull, kProfTotal, kProfSlots };
 
 template <int CG>
 struct Cfg {
@@ -96,6 +101,9 @@ struct alignas(64) TcArgs {
     int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
     float *peer_c[kMaxPeers];  // their C, laid out exactly like `c` (same offset and strides)
     DeviceStatus *status;
+    int dbg;          // timing experiments only (bit 0: converter moves no data, bit 1: no proxy fence,
+                      // bit 2: converter loads but does not store); results are wrong when set
+    long long *prof;  // optional: per-CTA wait-cycle counters (kProfSlots each), see ttb_tc_profile
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -108,11 +116,17 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // Time limit: 2 s of %globaltimer.  CLUSTER selects the cluster-scope acquire, needed
 // when arrivals come from the peer CTA.
 template <bool CLUSTER>
-__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                              long long *waited = nullptr) {
     unsigned long long t0 = 0;
+    const long long c0 = waited ? clock64() : 0;
     for (uint32_t i = 0;; ++i) {
-        const bool ok = CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
-        if (ok) return true;
+        (void)CLUSTER;  // arrivals from the peer CTA are waited for like local ones
+        const bool ok = mbar_try_wait(bar, parity);
+        if (ok) {
+            if (waited) *waited += clock64() - c0;
+            return true;
+        }
         if ((i & 63u) == 63u) {
             if (*abort_flag) return false;
             const unsigned long long now = global_ns();
@@ -162,6 +176,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
 
+    const long long kernel_t0 = clock64();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
@@ -230,13 +245,14 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             uint32_t phase = 0;
             bool ok = true;
             int issued = 0;
+            long long w_a = 0;
             for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
                 int b, tm, tn;
                 tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
                 const int m0 = tm * C::TILE_M + static_cast<int>(cta_rank) * BM;
                 const int n0 = tn * C::TILE_N + static_cast<int>(cta_rank) * BNC;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!wait_or_abort<PAIR>(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                    if (!wait_or_abort<PAIR>(&empty_bar[stage], phase ^ 1u, abort_flag, &w_a)) {
                         report(args.status, abort_flag, kErrProducerWait, static_cast<unsigned>(stage));
                         ok = false;
                         break;
@@ -274,6 +290,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 for (int i = 0; i < 100000; ++i)
                     if (mbar_try_wait(&full_bar[last], last_phase)) break;
             }
+            if (args.prof) args.prof[blockIdx.x * kProfSlots + kProfProducerEmpty] = w_a;
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -286,6 +303,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
+            long long w_a = 0, w_b = 0;
             // Shared-memory descriptor fields per operand major.
             //  K-major : 128-byte swizzle (16 B chunks); rows of 128 B, 8-row groups 1024 B
             //            apart (SBO); a K step of 8 fp32 advances the start address by 32 B
@@ -308,7 +326,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             }
             for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
                 for (int ch = 0; ch < num_chunks && ok; ++ch) {
-                    if (!wait_or_abort<PAIR>(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
+                    if (!wait_or_abort<PAIR>(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, &w_a)) {
                         report(args.status, abort_flag, kErrAccEmptyWait, static_cast<unsigned>(acc));
                         ok = false;
                         break;
@@ -318,7 +336,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     const int kb_begin = ch * k_chunk;
                     const int kb_end = (kb_begin + k_chunk < num_kb) ? kb_begin + k_chunk : num_kb;
                     for (int kb = kb_begin; kb < kb_end; ++kb) {
-                        if (!wait_or_abort<PAIR>(&conv_bar[sstage], sphase, abort_flag)) {
+                        if (!wait_or_abort<PAIR>(&conv_bar[sstage], sphase, abort_flag, &w_b)) {
                             report(args.status, abort_flag, kErrMmaWait, static_cast<unsigned>(stage));
                             ok = false;
                             break;
@@ -370,6 +388,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             mma_commit<CG>(smem_u32(&drain_bar));
             for (int i = 0; i < 1000000; ++i)
                 if (mbar_try_wait(&drain_bar, 0)) break;
+            if (args.prof) {
+                args.prof[blockIdx.x * kProfSlots + kProfMmaAccEmpty] = w_a;
+                args.prof[blockIdx.x * kProfSlots + kProfMmaConv] = w_b;
+            }
         }
       } else if (args.n_peers > 0) {
         // ------------------------------------------------------------ forwarding (warps 2-3)
@@ -469,11 +491,12 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         float sum[128];
         int oslot = 0;
         uint32_t ophase = 0;
+        long long w_a = 0;
         for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
             int b, tm, tn;
             tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
             for (int ch = 0; ch < num_chunks; ++ch) {
-                if (!wait_or_abort<PAIR>(&acc_full_bar[acc], acc_phase, abort_flag)) {
+                if (!wait_or_abort<PAIR>(&acc_full_bar[acc], acc_phase, abort_flag, &w_a)) {
                     if (lane == 0) report(args.status, abort_flag, kErrEpilogueWait, static_cast<unsigned>(acc));
                     ok = false;
                     break;
@@ -539,6 +562,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 }
             }
         }
+        if (args.prof && warp == C::FIRST_EPI_WARP && lane == 0) {
+            args.prof[blockIdx.x * kProfSlots + kProfEpiAccFull] = w_a;
+            args.prof[blockIdx.x * kProfSlots + kProfTotal] = clock64() - kernel_t0;
+        }
     } else {
         // ------------------------------------------------------------ converters
         if constexpr (PAIR) setmaxnreg_dec<72>();
@@ -549,6 +576,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         int sstage = 0;
         uint32_t sphase = 0;
         bool ok = true;
+        long long w_a = 0, w_b = 0, w_c = 0;
         const bool mask_big = args.mask_big != 0;
         uint32_t conv_remote[SMALL_STAGES] = {0, 0};
         if constexpr (PAIR) {
@@ -558,12 +586,13 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             for (int kb = 0; kb < num_kb; ++kb) {
                 // The small slot must have been released by the MMAs that last read it, and the
                 // raw slot must have landed.
-                if (!wait_or_abort<PAIR>(&small_empty_bar[sstage], sphase ^ 1u, abort_flag) ||
-                    !wait_or_abort<false>(&full_bar[stage], phase, abort_flag)) {
+                if (!wait_or_abort<PAIR>(&small_empty_bar[sstage], sphase ^ 1u, abort_flag, &w_a) ||
+                    !wait_or_abort<false>(&full_bar[stage], phase, abort_flag, &w_b)) {
                     if (lane == 0) report(args.status, abort_flag, kErrConverterWait, static_cast<unsigned>(stage));
                     ok = false;
                     break;
                 }
+                const long long busy0 = clock64();
                 uint4 *raw = reinterpret_cast<uint4 *>(tiles + stage * STAGE_BYTES);
                 uint4 *small = reinterpret_cast<uint4 *>(tiles + SMALL_RING_OFFSET + sstage * STAGE_BYTES);
                 // All loads of a batch are issued before the first dependent instruction, so
@@ -573,6 +602,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 constexpr int PER_THREAD = RAW_BYTES / 16 / NCT;  // 16 x 16-byte words
                 constexpr int BATCH = 8;
                 static_assert(PER_THREAD % BATCH == 0, "converter batches must tile the stage");
+                if (!(args.dbg & 1))
 #pragma unroll
                 for (int base = 0; base < PER_THREAD; base += BATCH) {
                     uint4 x[BATCH];
@@ -591,11 +621,12 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                         sm.y = __float_as_uint(__uint_as_float(x[u].y) - __uint_as_float(big.y)) + 0x1000u;
                         sm.z = __float_as_uint(__uint_as_float(x[u].z) - __uint_as_float(big.z)) + 0x1000u;
                         sm.w = __float_as_uint(__uint_as_float(x[u].w) - __uint_as_float(big.w)) + 0x1000u;
-                        small[ctid + (base + u) * NCT] = sm;
+                        if (!(args.dbg & 4)) small[ctid + (base + u) * NCT] = sm;
+                        else if (sm.x == 0x12345678u) small[0] = sm;
                         if (mask_big) raw[ctid + (base + u) * NCT] = big;
                     }
                 }
-                fence_proxy_async_smem();
+                if (!(args.dbg & 2)) fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     if constexpr (PAIR)
@@ -603,6 +634,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     else
                         mbar_arrive(&conv_bar[sstage]);
                 }
+                w_c += clock64() - busy0;
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
@@ -612,6 +644,11 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     sphase ^= 1u;
                 }
             }
+        }
+        if (args.prof && ctid == 0) {
+            args.prof[blockIdx.x * kProfSlots + kProfConvSmallEmpty] = w_a;
+            args.prof[blockIdx.x * kProfSlots + kProfConvFull] = w_b;
+            args.prof[blockIdx.x * kProfSlots + kProfConvBusy] = w_c;
         }
     }
 
@@ -755,6 +792,8 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
     for (int i = 0; i < n_peers; ++i) args.peer_c[i] = static_cast<float *>(peer_c[i]);
     int rc = device_status_ptr(p.device, &args.status);
     if (rc != TTB_OK) return rc;
+    args.prof = profile_ptr(p.device);
+    args.dbg = opt.dbg;
     int sms = 148;
     sm_count(p.device, &sms);
     if (opt.two_cta) return launch_cg<2>(p, args, sms);

@@ -31,16 +31,21 @@ struct Options {
     int splitk = 1;
     int two_cta = -1;  // -1 = choose by shape
     int mask_big = 0;
+    int tc_profile = 0;
+    int tc_debug = 0;
 };
 Options g_opt;
 
 constexpr int kMaxDevices = 64;
+constexpr int kProfCtas = 256;
+constexpr size_t kProfBytes = kProfCtas * 8 * sizeof(long long);
 struct DeviceState {
     bool init = false;
     int sms = 0;
     DeviceStatus *status = nullptr;
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
+    long long *prof = nullptr;  // kProfCtas x 8 wait-cycle counters of the tcgen05 kernel
     void *stage[3] = {nullptr, nullptr, nullptr};
     size_t stage_bytes[3] = {0, 0, 0};
 };
@@ -96,6 +101,10 @@ static int device_state(int device, DeviceState **out) {
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(status)");
         e = cudaMemset(d.status, 0, sizeof(DeviceStatus));
         if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(status)");
+        e = cudaMalloc(&d.prof, kProfBytes);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(profile)");
+        e = cudaMemset(d.prof, 0, kProfBytes);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(profile)");
         d.init = true;
     }
     *out = &d;
@@ -108,6 +117,13 @@ int device_status_ptr(int device, DeviceStatus **out) {
     if (rc != TTB_OK) return rc;
     *out = d->status;
     return TTB_OK;
+}
+
+long long *profile_ptr(int device) {
+    if (!g_opt.tc_profile) return nullptr;
+    DeviceState *d;
+    if (device_state(device, &d) != TTB_OK) return nullptr;
+    return d->prof;
 }
 
 int sm_count(int device, int *out) {
@@ -259,6 +275,7 @@ static F32Options f32_options(bool two_cta) {
     o.k_chunk = g_opt.k_chunk;
     o.two_cta = two_cta ? 1 : 0;
     o.mask_big = g_opt.mask_big;
+    o.dbg = g_opt.tc_debug;
     return o;
 }
 
@@ -521,6 +538,14 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         g_opt.mask_big = value != 0;
         return TTB_OK;
     }
+    if (!strcmp(key, "tc_profile")) {
+        g_opt.tc_profile = value != 0;
+        return TTB_OK;
+    }
+    if (!strcmp(key, "tc_debug")) {
+        g_opt.tc_debug = static_cast<int>(value);
+        return TTB_OK;
+    }
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
@@ -533,6 +558,7 @@ TTB_API int64_t ttb_get_option(const char *key) {
     if (!strcmp(key, "splitk")) return g_opt.splitk;
     if (!strcmp(key, "two_cta")) return g_opt.two_cta;
     if (!strcmp(key, "mask_big")) return g_opt.mask_big;
+    if (!strcmp(key, "tc_profile")) return g_opt.tc_profile;
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
@@ -561,6 +587,23 @@ TTB_API int ttb_check_device(int device_id) {
                   h.detail);
         return TTB_ETIMEOUT;
     }
+    return TTB_OK;
+}
+
+TTB_API int ttb_tc_profile(int device_id, int64_t *out, int ctas) {
+    DeviceState *d;
+    int rc = device_state(device_id, &d);
+    if (rc != TTB_OK) return rc;
+    if (!out || ctas < 1 || ctas > kProfCtas) {
+        set_error("ttb_tc_profile: need an output array for 1..%d CTAs", kProfCtas);
+        return TTB_EINVAL;
+    }
+    cudaError_t e = cudaSetDevice(device_id);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+    e = cudaMemcpy(out, d->prof, static_cast<size_t>(ctas) * 8 * sizeof(long long), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(profile)");
     return TTB_OK;
 }
 
