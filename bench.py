@@ -308,12 +308,14 @@ def run_ours(args):
         ms_per_step = elapsed_ms / args.steps
         value = FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
         # Tensor-pipe roofline of the dominant kernel: this GPU's share of the algorithmic flops
-        # over the kernel's own duration.  fp32 accuracy costs three TF32 passes, and dense TF32
-        # runs at half the measured bf16 rate, so the ceiling is bf16 / 2 / 3.
+        # over the kernel's own duration.  fp32 accuracy costs, per algorithmic multiply-add, one
+        # TF32 multiply-add (the cost of two bf16 ones: dense TF32 runs at half the bf16 rate) and
+        # two bf16 multiply-adds, i.e. four bf16 multiply-add times: the ceiling is bf16 / 4.
+        # The classic 3xTF32 scheme would cost six (bf16 / 2 / 3); that figure is reported too.
         share = (part.end - part.begin) / DIM
         achieved = FLOPS_PER_STEP * share / (kernel_ms * 1e-3) / 1e12
         bf16 = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
-        peak = bf16 / 2.0 / 3.0
+        peak = bf16 / 4.0
         # CPU baseline: the reference's CPU kernel on a bounded sample, one host core
         lib, kind = load_reference()
         rows = 2048
@@ -361,7 +363,8 @@ def run_ours(args):
                                        f"({'fused into the GEMM kernel, peer stores over NVLink' if args.exchange == 'fused' else 'NCCL all_gather + re-layout'})")
                        if world > 1 else "single GPU",
                        "l2": "operands (768 MiB with C) exceed the 126 MB L2; no explicit flush",
-                       "kernel": variant, "arithmetic": "3xTF32 split on tcgen05, fp32 accumulate"},
+                       "kernel": variant, "arithmetic": ("split precision on tcgen05: TF32 product of the high parts + two bf16 "
+                                      "correction products, fp32 accumulate in TMEM chunks, fp32 register sums")},
             "clocks": clocks,
             "e2e": {"value": FLOPS_PER_STEP / (e2e_s / e2e_steps) / 1e12, "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
@@ -369,8 +372,8 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                          "traffic": DRAM_TRAFFIC_PER_FULL_LAUNCH * share, "kernel_ms": kernel_ms,
-                         "peak_source": f"{peak_kind}: bf16 sustained {bf16} TFLOP/s / 2 (TF32) / 3 (passes)",
-                         "tf32_pipe_tflops": 3.0 * achieved, "hbm_gbs_algorithmic": BYTES_PER_STEP * share / (kernel_ms * 1e-3) / 1e9},
+                         "peak_source": f"{peak_kind}: bf16 sustained {bf16} TFLOP/s / 4 (one TF32 + two bf16 products per flop)",
+                         "tf32_derived_peak_3x": bf16 / 2.0 / 3.0, "frac_of_tf32_derived_peak_3x": achieved / (bf16 / 6.0), "hbm_gbs_algorithmic": BYTES_PER_STEP * share / (kernel_ms * 1e-3) / 1e9},
             "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": kind,
                              "sample": f"first {rows} of {DIM} lhs rows (1/{DIM // rows} of the product), {cpu_s:.1f} s",
                              "host_cores_available": os.cpu_count()},

@@ -73,7 +73,7 @@ typedef struct ttb_view {
 enum ttb_variant {
     TTB_VARIANT_AUTO = 0,
     TTB_VARIANT_SIMT = 1,         /* CUDA-core register-tiled kernel, any dtype/stride */
-    TTB_VARIANT_TCGEN05_3XTF32 = 2, /* f32: tcgen05 + TMEM + TMA, split-TF32 */
+    TTB_VARIANT_TCGEN05_3XTF32 = 2, /* f32: tcgen05 + TMEM + TMA, split precision, one CTA per tile */
     TTB_VARIANT_DMMA_F64 = 3,     /* f64: FP64 tensor-core (DMMA) kernel */
     TTB_VARIANT_SIMT_SPLITK = 4,  /* SIMT with K split over CTAs + scratch reduce */
     TTB_VARIANT_TCGEN05_2CTA = 5  /* f32: tcgen05 cta_group::2 (CTA pairs) */
@@ -185,7 +185,10 @@ TTB_API int ttb_last_variant(void);
 TTB_API int64_t ttb_launch_count(void);
 TTB_API const char *ttb_variant_name(int variant);
 /* Options: "force_variant" (enum ttb_variant; AUTO restores dispatch),
- * "tf32_terms" (3 = split-TF32, default; 1 = single TF32 pass, test only),
+ * "tf32_terms" (how the f32 tensor-core kernel reaches fp32-class accuracy:
+ * 2 = hybrid split, default: one TF32 product of the operands' high parts plus
+ * two bf16 products that add the low-part corrections; 3 = classic 3xTF32;
+ * 1 = a single TF32 pass, test only -- it misses the 1e-5 gate),
  * "k_chunk" (32-element K blocks accumulated inside the tensor core before the
  * partial sum is folded into fp32 registers; 0 = default of 8, -1 = whole K,
  * test only), "two_cta" (automatic dispatch: -1 = pick the CTA-pair kernel by

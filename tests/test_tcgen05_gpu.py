@@ -1,4 +1,7 @@
-"""Parity tests specific to the tcgen05 / TMEM / TMA f32 kernel (split-TF32).
+"""Parity tests specific to the tcgen05 / TMEM / TMA f32 kernel.  It has three arithmetic
+modes ("tf32_terms"): 2 = hybrid split, the default (TF32 product of the big parts plus two bf16
+correction products), 3 = classic 3xTF32, 1 = one TF32 pass (test only); and two tile forms
+(one CTA, CTA pair).
 
 The kernel is forced, so a view it cannot take is an error rather than a silent detour
 through the SIMT kernel.  Operand layouts cover the four major combinations that forward
@@ -15,9 +18,10 @@ pytestmark = pytest.mark.gpu
 F32_TOL = 1e-5
 
 
-@pytest.fixture()
-def forced(ttb, reset_options):
-    ttb.set_option("force_variant", int(ttb.Variant.TCGEN05_3XTF32))
+@pytest.fixture(params=["cta", "pair"])
+def forced(request, ttb, reset_options):
+    """Forces the tensor-core kernel, once as single-CTA tiles and once as CTA pairs."""
+    ttb.set_option("force_variant", int(ttb.Variant.TCGEN05_3XTF32 if request.param == "cta" else ttb.Variant.TCGEN05_2CTA))
     return ttb
 
 
@@ -56,14 +60,16 @@ def test_single_tf32_pass_is_exact_on_small_integers(forced, shape):
     forced.set_option("tf32_terms", 1)
     for name, (l, r) in layouts(dev(a), dev(b)).items():
         got = host(forced.batched_matmul(l, r))
-        assert forced.last_variant() == forced.Variant.TCGEN05_3XTF32
+        assert forced.last_variant() in (forced.Variant.TCGEN05_3XTF32, forced.Variant.TCGEN05_2CTA)
         assert np.array_equal(got, want), name
     forced.check_device(0)
 
 
+@pytest.mark.parametrize("terms", [2, 3])
 @pytest.mark.parametrize("shape", [(1, 128, 128, 128), (1, 379, 1147, 635), (4, 200, 300, 150), (1, 512, 4096, 256)])
-def test_split_tf32_meets_f32_tolerance_all_layouts(forced, shape):
+def test_split_meets_f32_tolerance_all_layouts(forced, shape, terms):
     B, N, K, M = shape
+    forced.set_option("tf32_terms", terms)
     rng = np.random.default_rng(32)
     a = rng.standard_normal((B, N, K)).astype(np.float32)
     b = rng.standard_normal((B, K, M)).astype(np.float32)
@@ -84,8 +90,38 @@ def test_single_pass_is_not_enough_and_split_is(forced):
     one = rel_to_max(host(forced.batched_matmul(dev(a), dev(b))), want)
     forced.set_option("tf32_terms", 3)
     three = rel_to_max(host(forced.batched_matmul(dev(a), dev(b))), want)
+    forced.set_option("tf32_terms", 2)
+    hybrid = rel_to_max(host(forced.batched_matmul(dev(a), dev(b))), want)
     assert one > F32_TOL
     assert three <= F32_TOL
+    assert hybrid <= F32_TOL
+
+
+def test_hybrid_bf16_tile_layouts_are_exact_on_small_integers(forced):
+    """The hybrid split's bf16 tiles (written by the converters, read by kind::f16 MMAs) in all
+    four operand layouts: with the layout-check switch the kernel adds bf16(A).bf16(B) to the
+    TF32 product, which on small integers must be exactly twice the product."""
+    rng = np.random.default_rng(38)
+    a = rng.integers(-9, 10, (2, 300, 100)).astype(np.float32)
+    b = rng.integers(-9, 10, (2, 100, 260)).astype(np.float32)
+    want = (2 * np.matmul(a.astype(np.float64), b.astype(np.float64))).astype(np.float32)
+    forced.set_option("tf32_terms", 2)
+    forced.set_option("tc_debug", 8)
+    for name, (l, r) in layouts(dev(a), dev(b)).items():
+        assert np.array_equal(host(forced.batched_matmul(l, r)), want), name
+    forced.check_device(0)
+
+
+def test_all_positive_operands_stay_inside_the_gate(forced):
+    """Sums that only grow are the worst case for the tensor core's truncating accumulator;
+    the chunked accumulation keeps them inside 1e-5."""
+    rng = np.random.default_rng(39)
+    a = np.abs(rng.standard_normal((1, 256, 8192))).astype(np.float32)
+    b = np.abs(rng.standard_normal((1, 8192, 256))).astype(np.float32)
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    for terms in (2, 3):
+        forced.set_option("tf32_terms", terms)
+        assert rel_to_max(host(forced.batched_matmul(dev(a), dev(b))), want) <= F32_TOL, terms
 
 
 def test_tensor_core_reads_fp32_words_as_truncated_tf32(forced):
@@ -95,6 +131,7 @@ def test_tensor_core_reads_fp32_words_as_truncated_tf32(forced):
     rng = np.random.default_rng(34)
     a = rng.standard_normal((1, 256, 512)).astype(np.float32)
     b = rng.standard_normal((1, 512, 256)).astype(np.float32)
+    forced.set_option("tf32_terms", 3)
     plain = host(forced.batched_matmul(dev(a), dev(b)))
     forced.set_option("mask_big", 1)
     masked = host(forced.batched_matmul(dev(a), dev(b)))

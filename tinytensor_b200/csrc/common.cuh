@@ -56,7 +56,8 @@ long long *profile_ptr(int device);
 // Per-dtype launchers.  Each returns a ttb_status.
 int launch_simt(const Problem &p, bool allow_splitk);
 struct F32Options {
-    int terms = 3;      // 3 = split-TF32; 1 = one TF32 pass (test only)
+    int terms = 2;      // 2 = hybrid split (TF32 big.big + two bf16 correction products, default);
+                        // 3 = classic 3xTF32; 1 = one TF32 pass (test only)
     int k_chunk = 0;    // K blocks accumulated in TMEM before folding into registers (0 = all)
     int two_cta = 0;    // use CTA pairs (cta_group::2)
     int mask_big = 0;   // converters also rewrite the raw tile with its masked big part (test only)

@@ -37,6 +37,7 @@
 // All waits are bounded: a wait that gives up writes an error word and the CTA unwinds
 // (TMEM freed) instead of hanging.
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include <cstdio>
 #include <cstring>
@@ -62,6 +63,7 @@ constexpr int STAGE_BYTES = RAW_BYTES;         // one slot of either ring
 constexpr int SMALL_RING_OFFSET = STAGES * STAGE_BYTES;
 constexpr int SMEM_BYTES = (STAGES + SMALL_STAGES) * STAGE_BYTES + 1024;  // + alignment slack
 constexpr int MN_BOX_BYTES = 32 * BK * 4;      // one MN-major TMA box: 32 (MN) x BK (K)
+constexpr int H_TILE_BYTES = BM * BK * 2;      // 8 KiB: one bf16 operand tile of the hybrid split
 constexpr int DEFAULT_K_CHUNK = 8;             // K blocks summed inside TMEM
 constexpr int kMaxPeers = 15;                  // fused all-gather: peers besides this GPU
 // Profile slots per CTA: cycles the producer waited for a free raw slot, the MMA thread for a
@@ -318,6 +320,13 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             const uint32_t b_lbo = args.b_mn_major ? MN_BOX_BYTES : 16, b_sbo = args.b_mn_major ? 512 : 1024;
             const uint32_t b_kstep = args.b_mn_major ? 1024 : 32;
             const uint64_t b_swz = args.b_mn_major ? kSwizzle128Base32 : kSwizzle128;
+            // bf16 tiles of the hybrid split (64-byte rows, 64-byte swizzle):
+            //  K-major : 8-row groups 512 B apart (SBO); a K step of 16 bf16 advances by 32 B.
+            //  MN-major: 32-element MN groups 2048 B apart (LBO), 8-row K groups 512 B apart
+            //            (SBO); a K step of 16 rows advances by 1024 B.
+            const uint32_t idesc16 = make_idesc_bf16(C::UMMA_M, C::UMMA_N, args.a_mn_major, args.b_mn_major);
+            const uint32_t a16_lbo = args.a_mn_major ? 2048 : 16, a16_kstep = args.a_mn_major ? 1024 : 32;
+            const uint32_t b16_lbo = args.b_mn_major ? 2048 : 16, b16_kstep = args.b_mn_major ? 1024 : 32;
             uint32_t peer_empty[STAGES], peer_small_empty[SMALL_STAGES], peer_acc_full[2];
             if constexpr (PAIR) {
                 for (int s = 0; s < STAGES; ++s) peer_empty[s] = mapa(smem_u32(&empty_bar[s]), 1);
@@ -346,6 +355,35 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                         const uint32_t b_raw = a_raw + TILE_BYTES;
                         const uint32_t a_small = tiles_base + SMALL_RING_OFFSET + sstage * STAGE_BYTES;
                         const uint32_t b_small = a_small + TILE_BYTES;
+                        if (args.terms == 2) {
+                            // Hybrid split: big.big on the raw fp32 tiles as TF32, the two
+                            // correction terms on bf16 tiles the converters wrote into the small
+                            // slot ([A small | A | B small | B], 8 KiB each).  Half the tensor
+                            // cycles of a TF32 correction term, half its shared-memory reads.
+#pragma unroll
+                            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                                const uint32_t fresh = (kb != kb_begin || kk != 0) ? 1u : 0u;
+                                mma_tf32<CG>(d_tmem, make_smem_desc(a_raw + kk * a_kstep, a_lbo, a_sbo, a_swz),
+                                             make_smem_desc(b_raw + kk * b_kstep, b_lbo, b_sbo, b_swz), idesc, fresh);
+                            }
+                            const uint32_t a_s16 = a_small, a_x16 = a_small + H_TILE_BYTES;
+                            const uint32_t b_s16 = a_small + 2 * H_TILE_BYTES, b_x16 = a_small + 3 * H_TILE_BYTES;
+                            if (!(args.dbg & 8)) {
+#pragma unroll
+                                for (int k2 = 0; k2 < BK / 16; ++k2) {
+                                    mma_f16<CG>(d_tmem, make_smem_desc(a_s16 + k2 * a16_kstep, a16_lbo, 512, kSwizzle64),
+                                                make_smem_desc(b_x16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16, 1);
+                                    mma_f16<CG>(d_tmem, make_smem_desc(a_x16 + k2 * a16_kstep, a16_lbo, 512, kSwizzle64),
+                                                make_smem_desc(b_s16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16, 1);
+                                }
+                            } else {
+                                // layout check only: bf16(A).bf16(B) on top of the TF32 product
+#pragma unroll
+                                for (int k2 = 0; k2 < BK / 16; ++k2)
+                                    mma_f16<CG>(d_tmem, make_smem_desc(a_x16 + k2 * a16_kstep, a16_lbo, 512, kSwizzle64),
+                                                make_smem_desc(b_x16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16, 1);
+                            }
+                        } else
 #pragma unroll
                         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                             const uint32_t fresh = (kb != kb_begin || kk != 0) ? 1u : 0u;
@@ -602,7 +640,55 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 constexpr int PER_THREAD = RAW_BYTES / 16 / NCT;  // 16 x 16-byte words
                 constexpr int BATCH = 8;
                 static_assert(PER_THREAD % BATCH == 0, "converter batches must tile the stage");
-                if (!(args.dbg & 1))
+                if (args.terms == 2) {
+                    // Hybrid split: per raw operand tile write two bf16 tiles, small = x - trunc_tf32(x)
+                    // and x itself, both rounded to nearest, in the 64-byte-swizzled layout the
+                    // bf16 MMAs read.  A 16-byte chunk of the raw tile (4 fp32) becomes 8 bytes in
+                    // each; where it goes follows from undoing the raw tile's swizzle:
+                    //  K-major  raw rows are 128 B with 16-B chunks XORed by (row & 7); the bf16 row
+                    //           is 64 B with 16-B chunks XORed by ((row >> 1) & 3) -- the XORs cancel
+                    //           up to the low bit, which picks the half of the 16-byte chunk.
+                    //  MN-major raw rows (one K index, 32 MN values) have 32-B chunks XORed by
+                    //           (k & 3); the bf16 row is 64 B with 16-B chunks XORed by ((k >> 1) & 3).
+                    const uint8_t *raw_b = tiles + stage * STAGE_BYTES;
+                    uint8_t *out_b = tiles + SMALL_RING_OFFSET + sstage * STAGE_BYTES;
+                    constexpr int PER_T = TILE_BYTES / 16 / NCT;  // 8 chunks per thread per operand tile
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const bool mn = half ? (args.b_mn_major != 0) : (args.a_mn_major != 0);
+                        const uint4 *rt = reinterpret_cast<const uint4 *>(raw_b + half * TILE_BYTES);
+                        uint8_t *s16 = out_b + half * 2 * H_TILE_BYTES;
+                        uint8_t *x16 = s16 + H_TILE_BYTES;
+                        uint4 x[PER_T];
+#pragma unroll
+                        for (int u = 0; u < PER_T; ++u) x[u] = rt[ctid + u * NCT];
+#pragma unroll
+                        for (int u = 0; u < PER_T; ++u) {
+                            const int ci = ctid + u * NCT;
+                            int dst;
+                            if (!mn) {
+                                const int r = ci >> 3, cp = ci & 7;
+                                dst = r * 64 + (cp >> 1) * 16 + (((cp ^ r) & 1) << 3);
+                            } else {
+                                const int box = ci >> 8, kr = (ci & 255) >> 3, c16 = ci & 7;
+                                const int lc = (c16 >> 1) ^ (kr & 3);
+                                dst = box * 2048 + kr * 64 + ((lc ^ ((kr >> 1) & 3)) << 4) + ((c16 & 1) << 3);
+                            }
+                            const float f0 = __uint_as_float(x[u].x), f1 = __uint_as_float(x[u].y);
+                            const float f2 = __uint_as_float(x[u].z), f3 = __uint_as_float(x[u].w);
+                            const float s0 = f0 - __uint_as_float(x[u].x & 0xFFFFE000u);
+                            const float s1 = f1 - __uint_as_float(x[u].y & 0xFFFFE000u);
+                            const float s2 = f2 - __uint_as_float(x[u].z & 0xFFFFE000u);
+                            const float s3 = f3 - __uint_as_float(x[u].w & 0xFFFFE000u);
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(s0, s1), p1 = __floats2bfloat162_rn(s2, s3);
+                            __nv_bfloat162 q0 = __floats2bfloat162_rn(f0, f1), q1 = __floats2bfloat162_rn(f2, f3);
+                            *reinterpret_cast<uint2 *>(s16 + dst) =
+                                make_uint2(*reinterpret_cast<uint32_t *>(&p0), *reinterpret_cast<uint32_t *>(&p1));
+                            *reinterpret_cast<uint2 *>(x16 + dst) =
+                                make_uint2(*reinterpret_cast<uint32_t *>(&q0), *reinterpret_cast<uint32_t *>(&q1));
+                        }
+                    }
+                } else if (!(args.dbg & 1))
 #pragma unroll
                 for (int base = 0; base < PER_THREAD; base += BATCH) {
                     uint4 x[BATCH];

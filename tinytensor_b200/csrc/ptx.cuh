@@ -301,5 +301,40 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n, int a_mn_ma
            (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// Same for kind::f16 with bf16 inputs (A/B format 1), fp32 accumulate.  K of one MMA is 16.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_major, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+           (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(m >> 4) << 24);
+}
+constexpr uint64_t kSwizzle64 = 4;
+
+// D[tmem] (+)= A * B with 16-bit inputs (kind::f16; the instruction descriptor says bf16).
+template <int CG>
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    if constexpr (CG == 1) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P;\n\t"
+            "setp.ne.b32 P, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, P;\n\t"
+            "}"
+            :
+            : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P;\n\t"
+            "setp.ne.b32 P, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, P;\n\t"
+            "}"
+            :
+            : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
 }  // namespace ptx
 }  // namespace ttb

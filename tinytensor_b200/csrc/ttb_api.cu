@@ -26,7 +26,7 @@ thread_local long long g_launches = 0;
 
 struct Options {
     int force_variant = TTB_VARIANT_AUTO;
-    int tf32_terms = 3;
+    int tf32_terms = 2;  // 2 = hybrid split (TF32 + two bf16 corrections), 3 = 3xTF32, 1 = one TF32 pass
     int k_chunk = 0;
     int splitk = 1;
     int two_cta = -1;  // -1 = choose by shape
@@ -507,8 +507,8 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         return TTB_OK;
     }
     if (!strcmp(key, "tf32_terms")) {
-        if (value != 1 && value != 3) {
-            set_error("tf32_terms must be 1 or 3");
+        if (value < 1 || value > 3) {
+            set_error("tf32_terms must be 1, 2 or 3");
             return TTB_EINVAL;
         }
         g_opt.tf32_terms = static_cast<int>(value);
