@@ -185,3 +185,46 @@ def test_ineligible_view_is_refused_when_forced_and_rerouted_when_not(forced):
     assert forced.last_variant() in (forced.Variant.SIMT, forced.Variant.SIMT_SPLITK)
     want = np.matmul(host(a).astype(np.float64), host(b).astype(np.float64))
     assert rel_to_max(host(out), want) <= F32_TOL
+
+
+def test_non_finite_operands_propagate_like_fp32(forced):
+    """Inf and NaN must come out where an fp32 product puts them (the split must not turn an
+    infinite result into NaN through Inf - Inf or 0 x Inf in its correction terms)."""
+    rng = np.random.default_rng(40)
+    a = rng.uniform(0.5, 1.5, (1, 128, 96)).astype(np.float32)
+    b = rng.uniform(0.5, 1.5, (1, 96, 160)).astype(np.float32)
+    a[0, 3, 7] = np.inf           # row 3 of C becomes +Inf (all of b[7, :] is positive)
+    a[0, 9, 11] = -np.inf         # row 9 becomes -Inf ...
+    b[0, 11, 5] = 0.0             # ... except column 5: -Inf * 0 = NaN
+    a[0, 20, 30] = np.nan         # row 20 becomes NaN
+    b[0, 40, 100] = np.inf        # column 100 becomes +Inf (a[:, 40] positive), NaN in row 20
+    with np.errstate(invalid="ignore", over="ignore"):
+        want = np.matmul(a.astype(np.float64), b.astype(np.float64)).astype(np.float32)
+    got = host(forced.batched_matmul(dev(a), dev(b)))
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.array_equal(np.isposinf(got), np.isposinf(want))
+    assert np.array_equal(np.isneginf(got), np.isneginf(want))
+    finite = np.isfinite(want)
+    assert np.abs(got[finite] - want[finite]).max() <= 1e-5 * np.abs(want[finite]).max()
+
+
+def test_wait_that_runs_out_is_reported_and_the_context_survives(forced):
+    """Failure detection without a GPU fault: a test switch makes the TMA producer arm its
+    first stage but never load it, so nothing ever completes that barrier.  Every wait in the
+    kernel is bounded (2 s): the roles give up, the kernel frees its TMEM and returns, the host
+    reads the error word, and the next call on the same context works."""
+    a = torch.randn((1, 256, 64), device="cuda")
+    b = torch.randn((1, 64, 256), device="cuda")
+    forced.check_device(0)
+    forced.set_option("tc_debug", 16)
+    forced.batched_matmul(a, b)
+    with pytest.raises(forced.TTBError) as info:
+        forced.check_device(0)
+    assert info.value.status == -6  # TTB_ETIMEOUT
+    assert "bounded wait" in str(info.value)
+    forced.set_option("tc_debug", 0)
+    forced.check_device(0)  # the error word was cleared by the read
+    out = forced.batched_matmul(a, b)
+    want = np.matmul(host(a).astype(np.float64), host(b).astype(np.float64))
+    assert rel_to_max(host(out), want) <= F32_TOL
+    forced.check_device(0)

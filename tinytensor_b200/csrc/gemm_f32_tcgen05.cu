@@ -1,12 +1,16 @@
 // gemm_f32_tcgen05.cu -- f32 batched GEMM on the 5th-generation tensor cores of sm_100a.
 //
-// C[b] = A[b] . B[b] in fp32-class accuracy from three TF32 tensor-core products
-// ("3xTF32").  kind::tf32 reads an fp32 word and ignores its low 13 mantissa bits, so
-// every operand x is split as x = big + small with big = x truncated to TF32 (which the
-// tensor core derives by itself from the raw word) and small = x - big (exact in fp32,
-// then rounded to nearest TF32).  Then
-//     A.B ~= small_A.big_B + big_A.small_B + big_A.big_B
-// and the dropped small.small term is below 2^-20 relative.
+// C[b] = A[b] . B[b] in fp32-class accuracy from split operands.  kind::tf32 reads an fp32
+// word and ignores its low 13 mantissa bits, so every operand x splits as x = big + small
+// with big = x truncated to TF32 (which the tensor core derives by itself from the raw word)
+// and small = x - big (exact in fp32).  Then A.B = big_A.big_B + small_A.B + big_A.small_B
+// up to a term below 2^-20 relative.  Two ways to add the two correction terms:
+//   hybrid (default, "tf32_terms" = 2): the converters write bf16(small) and bf16(x) tiles and
+//       the corrections run as bf16 MMAs (kind::f16): small_A.bf16(B) + bf16(A).small_B.
+//       A correction is ~2^-11 of the product, so bf16's 8 bits leave ~2^-19; a bf16 MMA costs
+//       half the tensor cycles and half the shared-memory reads of a TF32 one.
+//   3xTF32 ("tf32_terms" = 3): the converters write fp32 `small` tiles (rounded to nearest
+//       TF32) and the corrections run as TF32 MMAs: small_A.big_B + big_A.small_B.
 //
 // The tensor core's fp32 accumulator does not round to nearest: summing all of a long K
 // inside TMEM loses accuracy in proportion to K.  K is therefore cut into chunks (default
@@ -21,15 +25,16 @@
 //   warp 0       TMA producer: cp.async.bulk.tensor loads of the raw fp32 A and B tiles
 //                through tensor maps built from the operand's own strides (K-major or
 //                MN-major, so transposed views need no copy);
-//   warp 1       MMA issuer: one thread issues tcgen05.mma kind::tf32, three per K step,
-//                accumulating in TMEM; tcgen05.commit releases the stage / publishes the
-//                accumulator.  Warps 2-3 idle.
+//   warp 1       MMA issuer: one thread issues the tcgen05.mma instructions of a K block (TF32
+//                on the raw tiles, then the corrections), accumulating in TMEM;
+//                tcgen05.commit releases the stage / publishes the accumulator.
+//   warps 2-3    idle, or (fused all-gather) forward finished tiles to the peer GPUs' C.
 //   epilogue WG  (one per 128 accumulator columns): tcgen05.ld each chunk sum, add into
 //                registers, store C after the last chunk.  Two TMEM accumulators, so the
 //                read-out of chunk i overlaps the MMAs of chunk i+1.
-//   last WG      converters: read the raw tile from shared memory, write the `small` tile
-//                at the same offsets (the swizzled layout is preserved),
-//                fence.proxy.async, signal.
+//   last WG      converters: read the raw tile from shared memory, write the correction
+//                operands (bf16 tiles in their own swizzled layout, or fp32 `small` tiles at
+//                the same offsets), fence.proxy.async, signal.
 // Two forms: CG = 1, a 128x128 tile per CTA; CG = 2, a 256x256 tile per CTA pair
 // (cta_group::2): each CTA loads 128 rows of A and 128 columns of B and owns 128 rows of
 // the accumulator, which halves shared-memory and L2 traffic per flop.  No load carries a
@@ -103,8 +108,10 @@ struct alignas(64) TcArgs {
     int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
     float *peer_c[kMaxPeers];  // their C, laid out exactly like `c` (same offset and strides)
     DeviceStatus *status;
-    int dbg;          // timing experiments only (bit 0: converter moves no data, bit 1: no proxy fence,
-                      // bit 2: converter loads but does not store); results are wrong when set
+    int dbg;          // test / timing switches; results are wrong when set.  bit 0: converter moves no
+                      // data; 1: no proxy fence; 2: converter loads but does not store; 3: hybrid split
+                      // adds bf16(A).bf16(B) instead of the corrections (layout check); 4: the first
+                      // stage is never loaded (the bounded waits must run out and the kernel unwind)
     long long *prof;  // optional: per-CTA wait-cycle counters (kProfSlots each), see ttb_tc_profile
 };
 
@@ -142,6 +149,15 @@ __device__ __forceinline__ void report(DeviceStatus *st, volatile int *abort_fla
     if (atomicCAS(&st->error, 0u, code) == 0u) st->detail = detail;
     *abort_flag = 1;
     __threadfence_block();
+}
+
+// x -> (low part x - trunc_tf32(x), x itself) for the hybrid split's bf16 tiles; both zero
+// for Inf / NaN.
+__device__ __forceinline__ void split_operand(uint32_t bits, float &low, float &whole) {
+    const bool finite = (bits & 0x7F800000u) != 0x7F800000u;
+    const float f = __uint_as_float(bits);
+    low = finite ? f - __uint_as_float(bits & 0xFFFFE000u) : 0.0f;
+    whole = finite ? f : 0.0f;
 }
 
 // Tile order: groups of 8 row tiles sweep all column tiles, so the CTAs running
@@ -263,6 +279,16 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     uint8_t *b_dst = a_dst + TILE_BYTES;
                     mbar_arrive_expect_tx(&full_bar[stage], RAW_BYTES);
                     const int k0 = kb * BK;
+                    if ((args.dbg & 16) && issued == 0) {
+                        // Test switch: the very first stage is armed but never loaded, so the
+                        // waits downstream run out and the kernel must unwind by itself.
+                        ++issued;
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
                     if (args.a_mn_major) {
                         for (int j = 0; j < BM / 32; ++j)
                             tma_load_3d(a_dst + j * MN_BOX_BYTES, &args.tmap_a, &full_bar[stage], m0 + 32 * j, k0,
@@ -674,12 +700,15 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                                 const int lc = (c16 >> 1) ^ (kr & 3);
                                 dst = box * 2048 + kr * 64 + ((lc ^ ((kr >> 1) & 3)) << 4) + ((c16 & 1) << 3);
                             }
-                            const float f0 = __uint_as_float(x[u].x), f1 = __uint_as_float(x[u].y);
-                            const float f2 = __uint_as_float(x[u].z), f3 = __uint_as_float(x[u].w);
-                            const float s0 = f0 - __uint_as_float(x[u].x & 0xFFFFE000u);
-                            const float s1 = f1 - __uint_as_float(x[u].y & 0xFFFFE000u);
-                            const float s2 = f2 - __uint_as_float(x[u].z & 0xFFFFE000u);
-                            const float s3 = f3 - __uint_as_float(x[u].w & 0xFFFFE000u);
+                            // Inf and NaN travel through the TF32 product alone: in the bf16 tiles a
+                            // non-finite element is replaced by zero, otherwise Inf - Inf would make
+                            // its low part NaN and 0 x Inf would turn a correction term into NaN where
+                            // the fp32 result is +-Inf.
+                            float f0, f1, f2, f3, s0, s1, s2, s3;
+                            split_operand(x[u].x, s0, f0);
+                            split_operand(x[u].y, s1, f1);
+                            split_operand(x[u].z, s2, f2);
+                            split_operand(x[u].w, s3, f3);
                             __nv_bfloat162 p0 = __floats2bfloat162_rn(s0, s1), p1 = __floats2bfloat162_rn(s2, s3);
                             __nv_bfloat162 q0 = __floats2bfloat162_rn(f0, f1), q1 = __floats2bfloat162_rn(f2, f3);
                             *reinterpret_cast<uint2 *>(s16 + dst) =
