@@ -37,7 +37,10 @@ def _worker(rank, world, port, q):
 
         g = torch.Generator(device=dev).manual_seed(7)
         # column blocks: f32 (fused and NCCL exchange), ragged sizes included
-        for name, (n, k, m) in {"square": (1024, 512, 1024), "ragged": (1000, 520, 1300)}.items():
+        # "many_tiles": every CTA pair works through several tiles, so the tile-by-tile forwarding and
+        # the jointly forwarded last tile are both exercised
+        for name, (n, k, m) in {"square": (1024, 512, 1024), "ragged": (1000, 520, 1300),
+                                "many_tiles": (4096, 256, 8192)}.items():
             A = torch.randn((1, n, k), generator=g, device=dev)
             B = torch.randn((1, k, m), generator=g, device=dev)
             full = ttb.batched_matmul(A, B)

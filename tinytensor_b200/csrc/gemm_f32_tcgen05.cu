@@ -176,6 +176,66 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = in_g / gsz;
 }
 
+// Fused all-gather: copies this CTA's 128 rows of tile `t` from this GPU's C (just written by
+// the epilogue, still in L2) into the same place of every peer's C.  `tid` of `nthreads`
+// threads share the work; consecutive threads take consecutive 16-byte pieces of a row, so a
+// warp's store is one contiguous 512-byte piece of NVLink traffic.
+template <int CG>
+__device__ __forceinline__ void forward_tile(const TcArgs &args, int t, int cta_rank, int tid, int nthreads) {
+    using C = Cfg<CG>;
+    constexpr int ROW_VEC = C::TILE_N / 4;   // float4 per tile row
+    constexpr int TOTAL_VEC = BM * ROW_VEC;  // this CTA's 128 rows
+    constexpr int FWD_BATCH = 8;
+    const bool vec_ok = args.c_sj == 1 && (args.c_si & 3) == 0 && (args.c_sb & 3) == 0 &&
+                        (reinterpret_cast<uintptr_t>(args.c) & 15) == 0;
+    int b, tm, tn;
+    tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
+    const int row0 = tm * C::TILE_M + cta_rank * BM;
+    const int col0 = tn * C::TILE_N;
+    const long long base = static_cast<long long>(b) * args.c_sb;
+    if (vec_ok) {
+        for (int first = tid; first < TOTAL_VEC; first += nthreads * FWD_BATCH) {
+            float4 v[FWD_BATCH];
+            unsigned valid = 0;
+#pragma unroll
+            for (int u = 0; u < FWD_BATCH; ++u) {
+                const int idx = first + u * nthreads;
+                const int r = row0 + idx / ROW_VEC;
+                const int cc = col0 + (idx % ROW_VEC) * 4;
+                // whole vectors only; a ragged right edge is handled below
+                if (idx < TOTAL_VEC && r < args.N && cc + 4 <= args.M) {
+                    valid |= 1u << u;
+                    v[u] = __ldcg(reinterpret_cast<const float4 *>(args.c + base +
+                                                                   static_cast<long long>(r) * args.c_si + cc));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < FWD_BATCH; ++u) {
+                if (valid & (1u << u)) {
+                    const int idx = first + u * nthreads;
+                    const long long o = base + static_cast<long long>(row0 + idx / ROW_VEC) * args.c_si + col0 +
+                                        (idx % ROW_VEC) * 4;
+                    for (int pr = 0; pr < args.n_peers; ++pr) *reinterpret_cast<float4 *>(args.peer_c[pr] + o) = v[u];
+                }
+            }
+        }
+    }
+    // Scalar path: everything when the destination is not vector-aligned, else only the
+    // columns of a ragged right edge.
+    if (!vec_ok || (args.M & 3) != 0) {
+        const int edge_begin = vec_ok ? (args.M - (args.M & 3)) : 0;
+        for (int idx = tid; idx < BM * C::TILE_N; idx += nthreads) {
+            const int r = row0 + idx / C::TILE_N;
+            const int cc = col0 + idx % C::TILE_N;
+            if (r < args.N && cc < args.M && cc >= edge_begin) {
+                const long long o = base + static_cast<long long>(r) * args.c_si + static_cast<long long>(cc) * args.c_sj;
+                const float x = __ldcg(args.c + o);
+                for (int pr = 0; pr < args.n_peers; ++pr) args.peer_c[pr][o] = x;
+            }
+        }
+    }
+}
+
 template <int CG>
 __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const __grid_constant__ TcArgs args) {
     using C = Cfg<CG>;
@@ -190,6 +250,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     __shared__ uint64_t acc_empty_bar[2];   // accumulator read out (lives in the leader CTA)
     __shared__ uint64_t out_full_bar[2];    // tile stored into this GPU's C (epilogue -> forwarding warps)
     __shared__ uint64_t out_empty_bar[2];   // tile forwarded to every peer (forwarding warps -> epilogue)
+    __shared__ uint64_t last_full_bar;      // the CTA's last tile stored into this GPU's C
     __shared__ uint64_t drain_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
@@ -224,6 +285,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             mbar_init(&out_full_bar[a], 4 * C::EPI_WGS);
             mbar_init(&out_empty_bar[a], 2);
         }
+        mbar_init(&last_full_bar, 4 * C::EPI_WGS);
         mbar_init(&drain_bar, 1);
         abort_flag_s = 0;
         fence_mbar_init();
@@ -465,69 +527,19 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         // NVLink).  They are the only threads that NVLink back-pressure can stall; the MMA,
         // converter and epilogue warps keep going, so the exchange overlaps the math tile by
         // tile.  The two-slot full/empty handshake keeps the epilogue at most two tiles ahead.
+        // The CTA's LAST tile is not forwarded here: nothing is left to overlap it with, so all
+        // warps of the CTA push it together after their own loops (see below).
         const int stid = threadIdx.x - 64;                    // 0..63
-        constexpr int ROW_VEC = C::TILE_N / 4;                // float4 per tile row
-        constexpr int TOTAL_VEC = BM * ROW_VEC;               // this CTA's 128 rows
-        constexpr int FWD_BATCH = 8;
-        const bool vec_ok = args.c_sj == 1 && (args.c_si & 3) == 0 && (args.c_sb & 3) == 0 &&
-                            (reinterpret_cast<uintptr_t>(args.c) & 15) == 0;
         int oslot = 0;
         uint32_t ophase = 0;
         bool ok = true;
-        for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
-            int b, tm, tn;
-            tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
+        for (int t = first_tile; t + tile_step < args.total_tiles && ok; t += tile_step) {
             if (!wait_or_abort<false>(&out_full_bar[oslot], ophase, abort_flag)) {
                 if (lane == 0) report(args.status, abort_flag, kErrForwardWait, 16u + static_cast<unsigned>(oslot));
                 ok = false;
                 break;
             }
-            const int row0 = tm * C::TILE_M + static_cast<int>(cta_rank) * BM;
-            const int col0 = tn * C::TILE_N;
-            const long long base = static_cast<long long>(b) * args.c_sb;
-            if (vec_ok) {
-                for (int it = 0; it < TOTAL_VEC / 64; it += FWD_BATCH) {
-                    float4 v[FWD_BATCH];
-                    unsigned valid = 0;
-#pragma unroll
-                    for (int u = 0; u < FWD_BATCH; ++u) {
-                        const int idx = stid + (it + u) * 64;
-                        const int r = row0 + idx / ROW_VEC;
-                        const int cc = col0 + (idx % ROW_VEC) * 4;
-                        // whole vectors only; a ragged right edge is handled below
-                        if (r < args.N && cc + 4 <= args.M) {
-                            valid |= 1u << u;
-                            v[u] = __ldcg(reinterpret_cast<const float4 *>(
-                                args.c + base + static_cast<long long>(r) * args.c_si + cc));
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < FWD_BATCH; ++u) {
-                        if (valid & (1u << u)) {
-                            const int idx = stid + (it + u) * 64;
-                            const long long o = base + static_cast<long long>(row0 + idx / ROW_VEC) * args.c_si +
-                                                col0 + (idx % ROW_VEC) * 4;
-                            for (int pr = 0; pr < args.n_peers; ++pr)
-                                *reinterpret_cast<float4 *>(args.peer_c[pr] + o) = v[u];
-                        }
-                    }
-                }
-            }
-            // Scalar path: everything when the destination is not vector-aligned, else only
-            // the columns of a ragged right edge.
-            if (!vec_ok || (args.M & 3) != 0) {
-                const int edge_begin = vec_ok ? (args.M - (args.M & 3)) : 0;
-                for (int idx = stid; idx < BM * C::TILE_N; idx += 64) {
-                    const int r = row0 + idx / C::TILE_N;
-                    const int cc = col0 + idx % C::TILE_N;
-                    if (r < args.N && cc < args.M && cc >= edge_begin) {
-                        const long long o = base + static_cast<long long>(r) * args.c_si +
-                                            static_cast<long long>(cc) * args.c_sj;
-                        const float x = __ldcg(args.c + o);
-                        for (int pr = 0; pr < args.n_peers; ++pr) args.peer_c[pr][o] = x;
-                    }
-                }
-            }
+            forward_tile<CG>(args, t, static_cast<int>(cta_rank), stid, 64);
             __syncwarp();
             if (lane == 0) mbar_arrive(&out_empty_bar[oslot]);
             if (++oslot == 2) {
@@ -619,7 +631,11 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 // Publish the tile (now in this GPU's C) to the forwarding warps.
                 __threadfence();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&out_full_bar[oslot]);
+                // The CTA's last tile has its own single-phase barrier: the threads that forward
+                // it have not followed the two-slot ring, and a parity wait is only meaningful to
+                // a waiter that is at most one phase behind.
+                const bool last_tile = t + tile_step >= args.total_tiles;
+                if (lane == 0) mbar_arrive(last_tile ? &last_full_bar : &out_full_bar[oslot]);
                 if (++oslot == 2) {
                     oslot = 0;
                     ophase ^= 1u;
@@ -765,6 +781,21 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             args.prof[blockIdx.x * kProfSlots + kProfConvFull] = w_b;
             args.prof[blockIdx.x * kProfSlots + kProfConvBusy] = w_c;
         }
+    }
+
+    // ---------------------------------------------------------------- fused all-gather, last tile
+    // Every warp is done with its role by the time it gets here; the CTA's last tile has no
+    // further math to hide behind, so all of them forward it.
+    if (args.n_peers > 0 && first_tile < args.total_tiles) {
+        const int n_mine = (args.total_tiles - first_tile + tile_step - 1) / tile_step;
+        const int j = n_mine - 1;
+        if (wait_or_abort<false>(&last_full_bar, 0u, abort_flag)) {
+            forward_tile<CG>(args, first_tile + j * tile_step, static_cast<int>(cta_rank), threadIdx.x, C::NUM_THREADS);
+        } else if (threadIdx.x == 0) {
+            report(args.status, abort_flag, kErrForwardWait, 32u);
+        }
+        // Peer stores must have left this GPU before the kernel is reported complete.
+        __threadfence_system();
     }
 
     // ---------------------------------------------------------------- teardown
