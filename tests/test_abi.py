@@ -42,7 +42,7 @@ def test_options_round_trip_and_reject_bad_values(ttb, reset_options):
     with pytest.raises(ttb.TTBError):
         ttb.set_option("force_variant", 77)
     with pytest.raises(ttb.TTBError):
-        ttb.set_option("tf32_terms", 2)
+        ttb.set_option("tf32_terms", 4)
     with pytest.raises(ttb.TTBError):
         ttb.set_option("no_such_option", 1)
 
