@@ -272,11 +272,14 @@ def test_config4_large_square_f32_sampled_rows(ttb):
     want = (A[0, rows].double() @ B[0].double()).cpu().numpy()
     got = C[0, rows].cpu().numpy()
     assert rel_to_max(got, want) <= F32_TOL
-    # column-block form used by the partitioner gives the same bits as the full product
+    # The column-block form used by the partitioner.  Not bit-identical to the full product: a
+    # block's tile count need not fill the GPU, then K is dealt out differently (stream-K) and the
+    # fp32 partial sums associate differently.  Both stay far inside the gate.
     C2 = torch.empty_like(C)
     for c0 in range(0, n, 2048):
         ttb.batched_matmul(A, B[:, :, c0:c0 + 2048], out=C2[:, :, c0:c0 + 2048])
-    assert torch.equal(C, C2)
+    assert float((C - C2).abs().max() / C.abs().max()) <= 2e-6
+    assert rel_to_max(C2[0, rows].cpu().numpy(), want) <= F32_TOL
 
 
 def test_config4b_f64_4096(ttb):

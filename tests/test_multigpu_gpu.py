@@ -1,7 +1,7 @@
 """Multi-GPU parity of the partitioner on real devices (skipped with fewer than two GPUs):
 one process per GPU over NCCL.  The column-block product with the all-gather fused into the
-GEMM kernel, and the NCCL all-gather form, must both reproduce the single-GPU product bit for
-bit; batch-sharded products must equal the unsharded ones."""
+GEMM kernel, and the NCCL all-gather form, must agree with each other bit for bit and with the
+single-GPU product to a few ulp of max|C|; batch-sharded products must equal the unsharded ones."""
 import os
 import socket
 import sys
@@ -49,9 +49,14 @@ def _worker(rank, world, port, q):
             C.fill_(float("nan"))
             torch.cuda.synchronize()
             dist.barrier()
-            results[f"{name}_fused"] = bool(torch.equal(fused(A, B, out=C), full))
+            # a shard's K blocks may be dealt out differently from the full product's (stream-K),
+            # so sums associate differently: equal to within a few ulp of max|C|, not bit-equal
+            close = lambda x: bool(float((x - full).abs().max() / full.abs().max()) <= 2e-6)
+            results[f"{name}_fused"] = close(fused(A, B, out=C))
             plain = ttb.ShardedMatmul()
-            results[f"{name}_nccl"] = bool(torch.equal(plain(A, B), full))
+            results[f"{name}_nccl"] = close(plain(A, B))
+            # both exchanges deliver the same shards: bit-equal to each other
+            results[f"{name}_fused_eq_nccl"] = bool(torch.equal(fused(A, B, out=C), plain(A, B)))
         # column blocks, integer dtype: goes through the NCCL exchange, bit-exact
         Ai = torch.randint(-8, 9, (1, 300, 128), generator=g, device=dev, dtype=torch.int32)
         Bi = torch.randint(-8, 9, (1, 128, 512), generator=g, device=dev, dtype=torch.int32)

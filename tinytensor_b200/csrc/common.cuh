@@ -39,7 +39,8 @@ enum DeviceErrorCode : unsigned int {
     kErrMmaWait = 3,
     kErrEpilogueWait = 4,
     kErrAccEmptyWait = 5,
-    kErrForwardWait = 6
+    kErrForwardWait = 6,
+    kErrStreamKWait = 7
 };
 
 void set_error(const char *fmt, ...);
@@ -52,6 +53,9 @@ int sm_count(int device, int *out);
 // Device buffer for the tcgen05 kernel's wait-cycle counters, or nullptr when the
 // "tc_profile" option is off.
 long long *profile_ptr(int device);
+// Stream-K workspace (partial-sum slots, ready flags) of (device, stream) and this launch's number.
+int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags,
+                      unsigned int *epoch);
 
 // Per-dtype launchers.  Each returns a ttb_status.
 int launch_simt(const Problem &p, bool allow_splitk);
@@ -62,6 +66,7 @@ struct F32Options {
     int two_cta = 0;    // use CTA pairs (cta_group::2)
     int mask_big = 0;   // converters also rewrite the raw tile with its masked big part (test only)
     int dbg = 0;        // timing experiments (wrong results when non-zero)
+    int streamk = -1;   // K blocks dealt out evenly over the SMs: -1 automatic, 0 never, 1 whenever possible
 };
 // n_peers > 0 fuses an all-gather into the product: every finished tile is also stored into
 // peer_c[i] (peer-mapped pointers to the other GPUs' C, same layout as p.c).

@@ -105,6 +105,10 @@ struct alignas(64) TcArgs {
     int terms;     // 3 = split-TF32, 1 = single pass (test only)
     int k_chunk;   // K blocks per TMEM accumulation chunk
     int mask_big;  // converters also overwrite the raw tile with its masked big part
+    int streamk;   // 1: K blocks are dealt out evenly over the units (see Work), else whole tiles
+    float *sk_partials;       // stream-K workspace: per unit, CTA and epilogue warp 32 x 128 partial sums
+    unsigned int *sk_flags;   // stream-K flags, one per unit, CTA and epilogue warp: launch number when ready
+    unsigned int sk_epoch;    // this launch's number
     int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
     float *peer_c[kMaxPeers];  // their C, laid out exactly like `c` (same offset and strides)
     DeviceStatus *status;
@@ -175,6 +179,19 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tm = first_m + in_g % gsz;
     tn = in_g / gsz;
 }
+
+// Work distribution over the resident units (CTAs, or CTA pairs).
+//  whole tiles: unit u takes tiles u, u + units, u + 2 units, ... with all of K.
+//  stream-K   : the tile-major sequence of all K blocks of all tiles is cut into `units` equal
+//               contiguous ranges, so every unit gets the same amount of work whatever the tile
+//               count.  A range falls into segments (tile, [kb0, kb1)), listed in shared memory
+//               at kernel start (at most kMaxSegments; the host only picks stream-K when that
+//               holds).  A segment with kb0 == 0 owns its tile: it stores C, after adding the
+//               partial sums of the units whose ranges start inside the tile.  A segment with
+//               kb0 > 0 (always the first of its range) writes its partial sums to a workspace
+//               and raises a flag.  Owners wait only for units that do that work first, so no
+//               wait is circular.
+constexpr int kMaxSegments = 16;
 
 // Fused all-gather: copies this CTA's 128 rows of tile `t` from this GPU's C (just written by
 // the epilogue, still in L2) into the same place of every peer's C.  `tid` of `nthreads`
@@ -253,6 +270,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     __shared__ uint64_t last_full_bar;      // the CTA's last tile stored into this GPU's C
     __shared__ uint64_t drain_bar;
     __shared__ uint32_t tmem_base_slot;
+    __shared__ int seg_tile_s[kMaxSegments], seg_kb0_s[kMaxSegments], seg_kb1_s[kMaxSegments], seg_count_s;
     __shared__ int abort_flag_s;
 
     const long long kernel_t0 = clock64();
@@ -287,6 +305,26 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         }
         mbar_init(&last_full_bar, 4 * C::EPI_WGS);
         mbar_init(&drain_bar, 1);
+        if (args.streamk) {
+            // cut this unit's K-block range into per-tile segments
+            const int nkb = (args.K + BK - 1) / BK;
+            const int u = PAIR ? (blockIdx.x >> 1) : blockIdx.x, us = PAIR ? (gridDim.x >> 1) : gridDim.x;
+            const long long all = static_cast<long long>(args.total_tiles) * nkb;  // < 2^31, checked by the host
+            int pos = static_cast<int>(all * u / us);
+            const int end = static_cast<int>(all * (u + 1) / us);
+            int n = 0;
+            while (pos < end && n < kMaxSegments) {
+                const int tile = pos / nkb, k0 = pos - tile * nkb;
+                int stop = pos + (nkb - k0);
+                if (stop > end) stop = end;
+                seg_tile_s[n] = tile;
+                seg_kb0_s[n] = k0;
+                seg_kb1_s[n] = k0 + (stop - pos);
+                ++n;
+                pos = stop;
+            }
+            seg_count_s = n;
+        }
         abort_flag_s = 0;
         fence_mbar_init();
         tma_prefetch_desc(&args.tmap_a);
@@ -308,9 +346,38 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 
     const int num_kb = (args.K + BK - 1) / BK;
     const int k_chunk = args.k_chunk > 0 ? args.k_chunk : num_kb;
-    const int num_chunks = (num_kb + k_chunk - 1) / k_chunk;
-    const int first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
-    const int tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
+    const int unit = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+    const int units = PAIR ? (gridDim.x >> 1) : gridDim.x;
+    // This unit's segments.  n_store of them store C (all of them with whole tiles); the fused
+    // all-gather treats the last stored tile specially.
+    int n_seg, n_store, last_store_tile;
+    if (!args.streamk) {
+        n_seg = unit < args.total_tiles ? (args.total_tiles - unit + units - 1) / units : 0;
+        n_store = n_seg;
+        last_store_tile = unit + (n_seg - 1) * units;
+    } else {
+        n_seg = seg_count_s;
+        n_store = 0;
+        last_store_tile = -1;
+        for (int i = 0; i < n_seg; ++i) {
+            if (seg_kb0_s[i] == 0) {
+                ++n_store;
+                last_store_tile = seg_tile_s[i];
+            }
+        }
+    }
+    // Segment i of this unit: (tile, [kb0, kb1)).
+    auto segment = [&](int i, int &tile, int &kb0, int &kb1) {
+        if (!args.streamk) {
+            tile = unit + i * units;
+            kb0 = 0;
+            kb1 = num_kb;
+        } else {
+            tile = seg_tile_s[i];
+            kb0 = seg_kb0_s[i];
+            kb1 = seg_kb1_s[i];
+        }
+    };
 
     // Register budget per warpgroup (CTA-pair form: 512 threads start with 128 registers
     // each; the epilogue holds 128 accumulators per thread and takes registers the other
@@ -326,12 +393,14 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             bool ok = true;
             int issued = 0;
             long long w_a = 0;
-            for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
+            for (int seg = 0; seg < n_seg && ok; ++seg) {
+                int t, kb0, kb1;
+                segment(seg, t, kb0, kb1);
                 int b, tm, tn;
                 tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
                 const int m0 = tm * C::TILE_M + static_cast<int>(cta_rank) * BM;
                 const int n0 = tn * C::TILE_N + static_cast<int>(cta_rank) * BNC;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!wait_or_abort<PAIR>(&empty_bar[stage], phase ^ 1u, abort_flag, &w_a)) {
                         report(args.status, abort_flag, kErrProducerWait, static_cast<unsigned>(stage));
                         ok = false;
@@ -421,8 +490,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 for (int s = 0; s < SMALL_STAGES; ++s) peer_small_empty[s] = mapa(smem_u32(&small_empty_bar[s]), 1);
                 for (int a = 0; a < 2; ++a) peer_acc_full[a] = mapa(smem_u32(&acc_full_bar[a]), 1);
             }
-            for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
-                for (int ch = 0; ch < num_chunks && ok; ++ch) {
+            for (int seg = 0; seg < n_seg && ok; ++seg) {
+                int t, kb0, kb1;
+                segment(seg, t, kb0, kb1);
+                for (int kb_begin = kb0; kb_begin < kb1 && ok; kb_begin += k_chunk) {
                     if (!wait_or_abort<PAIR>(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, &w_a)) {
                         report(args.status, abort_flag, kErrAccEmptyWait, static_cast<unsigned>(acc));
                         ok = false;
@@ -430,8 +501,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * C::ACC_COLS);
-                    const int kb_begin = ch * k_chunk;
-                    const int kb_end = (kb_begin + k_chunk < num_kb) ? kb_begin + k_chunk : num_kb;
+                    const int kb_end = (kb_begin + k_chunk < kb1) ? kb_begin + k_chunk : kb1;
                     for (int kb = kb_begin; kb < kb_end; ++kb) {
                         if (!wait_or_abort<PAIR>(&conv_bar[sstage], sphase, abort_flag, &w_b)) {
                             report(args.status, abort_flag, kErrMmaWait, static_cast<unsigned>(stage));
@@ -533,7 +603,12 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         int oslot = 0;
         uint32_t ophase = 0;
         bool ok = true;
-        for (int t = first_tile; t + tile_step < args.total_tiles && ok; t += tile_step) {
+        int stored = 0;
+        for (int seg = 0; seg < n_seg && ok; ++seg) {
+            int t, kb0, kb1;
+            segment(seg, t, kb0, kb1);
+            if (kb0 != 0) continue;             // a partial-sum segment stores nothing into C
+            if (++stored == n_store) break;     // the last stored tile is forwarded by every warp
             if (!wait_or_abort<false>(&out_full_bar[oslot], ophase, abort_flag)) {
                 if (lane == 0) report(args.status, abort_flag, kErrForwardWait, 16u + static_cast<unsigned>(oslot));
                 ok = false;
@@ -568,10 +643,16 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         int oslot = 0;
         uint32_t ophase = 0;
         long long w_a = 0;
-        for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
+        // Stream-K workspace of this warp: [unit][CTA of the pair][epilogue warp][lane][128 floats].
+        const int epi_warp = warp - C::FIRST_EPI_WARP;
+        constexpr int EPI_WARPS = 4 * C::EPI_WGS;
+        int stored = 0;
+        for (int seg = 0; seg < n_seg && ok; ++seg) {
+            int t, kb0, kb1;
+            segment(seg, t, kb0, kb1);
             int b, tm, tn;
             tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
-            for (int ch = 0; ch < num_chunks; ++ch) {
+            for (int ch = kb0; ch < kb1; ch += k_chunk) {
                 if (!wait_or_abort<PAIR>(&acc_full_bar[acc], acc_phase, abort_flag, &w_a)) {
                     if (lane == 0) report(args.status, abort_flag, kErrEpilogueWait, static_cast<unsigned>(acc));
                     ok = false;
@@ -580,7 +661,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 tc_fence_after_sync();
                 const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * C::ACC_COLS + col_half * 128) +
                                        (static_cast<uint32_t>(quarter * 32) << 16);
-                const bool first = ch == 0;
+                const bool first = ch == kb0;
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     uint32_t v[16];
@@ -604,6 +685,55 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 if (acc == 0) acc_phase ^= 1u;
             }
             if (!ok) break;
+            if (kb0 != 0) {
+                // Stream-K, a range that starts inside a tile: hand the partial sums to the unit
+                // that owns the tile.  Warp w of the owner reads exactly what warp w wrote here
+                // (same TMEM lanes, same columns), so one flag per warp is all the ordering needed.
+                const long long slot = (static_cast<long long>(unit) * CG + cta_rank) * EPI_WARPS + epi_warp;
+                float4 *dst = reinterpret_cast<float4 *>(args.sk_partials + (slot * 32 + lane) * 128);
+#pragma unroll
+                for (int q = 0; q < 32; ++q) dst[q] = make_float4(sum[4 * q], sum[4 * q + 1], sum[4 * q + 2], sum[4 * q + 3]);
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicExch(&args.sk_flags[slot], args.sk_epoch);
+                continue;
+            }
+            if (kb1 != num_kb) {
+                // Stream-K, the owner of a tile whose tail other units computed: add their sums.
+                const long long all_kb = static_cast<long long>(args.total_tiles) * num_kb;
+                for (int q = unit + 1; q < units && ok; ++q) {
+                    if (all_kb * q / units >= static_cast<long long>(t + 1) * num_kb) break;
+                    const long long slot = (static_cast<long long>(q) * CG + cta_rank) * EPI_WARPS + epi_warp;
+                    unsigned long long t0 = 0;
+                    for (uint32_t spin = 0;; ++spin) {
+                        if (*reinterpret_cast<volatile unsigned int *>(&args.sk_flags[slot]) == args.sk_epoch) break;
+                        if ((spin & 63u) == 63u) {
+                            const unsigned long long now = global_ns();
+                            if (t0 == 0) t0 = now;
+                            if (*abort_flag || now - t0 > 2000000000ull) {
+                                ok = false;
+                                break;
+                            }
+                        }
+                    }
+                    if (!ok) {
+                        if (lane == 0) report(args.status, abort_flag, kErrStreamKWait, static_cast<unsigned>(q));
+                        break;
+                    }
+                    __threadfence();
+                    const float4 *src = reinterpret_cast<const float4 *>(args.sk_partials + (slot * 32 + lane) * 128);
+#pragma unroll
+                    for (int v = 0; v < 32; ++v) {
+                        const float4 p = __ldcg(src + v);
+                        sum[4 * v] += p.x;
+                        sum[4 * v + 1] += p.y;
+                        sum[4 * v + 2] += p.z;
+                        sum[4 * v + 3] += p.w;
+                    }
+                }
+                if (!ok) break;
+            }
+            ++stored;
             const int row = tm * C::TILE_M + static_cast<int>(cta_rank) * BM + quarter * 32 + lane;
             const int col0 = tn * C::TILE_N + col_half * 128;
             if (args.n_peers > 0) {
@@ -634,7 +764,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 // The CTA's last tile has its own single-phase barrier: the threads that forward
                 // it have not followed the two-slot ring, and a parity wait is only meaningful to
                 // a waiter that is at most one phase behind.
-                const bool last_tile = t + tile_step >= args.total_tiles;
+                const bool last_tile = stored == n_store;
                 if (lane == 0) mbar_arrive(last_tile ? &last_full_bar : &out_full_bar[oslot]);
                 if (++oslot == 2) {
                     oslot = 0;
@@ -662,8 +792,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         if constexpr (PAIR) {
             for (int s = 0; s < SMALL_STAGES; ++s) conv_remote[s] = mapa(smem_u32(&conv_bar[s]), 0);
         }
-        for (int t = first_tile; t < args.total_tiles && ok; t += tile_step) {
-            for (int kb = 0; kb < num_kb; ++kb) {
+        for (int seg = 0; seg < n_seg && ok; ++seg) {
+            int t, kb0, kb1;
+            segment(seg, t, kb0, kb1);
+            for (int kb = kb0; kb < kb1; ++kb) {
                 // The small slot must have been released by the MMAs that last read it, and the
                 // raw slot must have landed.
                 if (!wait_or_abort<PAIR>(&small_empty_bar[sstage], sphase ^ 1u, abort_flag, &w_a) ||
@@ -786,11 +918,9 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     // ---------------------------------------------------------------- fused all-gather, last tile
     // Every warp is done with its role by the time it gets here; the CTA's last tile has no
     // further math to hide behind, so all of them forward it.
-    if (args.n_peers > 0 && first_tile < args.total_tiles) {
-        const int n_mine = (args.total_tiles - first_tile + tile_step - 1) / tile_step;
-        const int j = n_mine - 1;
+    if (args.n_peers > 0 && n_store > 0) {
         if (wait_or_abort<false>(&last_full_bar, 0u, abort_flag)) {
-            forward_tile<CG>(args, first_tile + j * tile_step, static_cast<int>(cta_rank), threadIdx.x, C::NUM_THREADS);
+            forward_tile<CG>(args, last_store_tile, static_cast<int>(cta_rank), threadIdx.x, C::NUM_THREADS);
         } else if (threadIdx.x == 0) {
             report(args.status, abort_flag, kErrForwardWait, 32u);
         }
@@ -846,7 +976,7 @@ bool plan(const Problem &p, TcPlan *pl, char *why, int why_len) {
 }
 
 template <int CG>
-int launch_cg(const Problem &p, TcArgs &args, int sms) {
+int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     using C = Cfg<CG>;
     args.tiles_m = static_cast<int>((p.N + C::TILE_M - 1) / C::TILE_M);
     args.tiles_n = static_cast<int>((p.M + C::TILE_N - 1) / C::TILE_N);
@@ -885,7 +1015,24 @@ int launch_cg(const Problem &p, TcArgs &args, int sms) {
         }
         if (units > max_clusters[p.device & 63]) units = max_clusters[p.device & 63];
     }
-    if (units > args.total_tiles) units = args.total_tiles;
+    // Whole tiles per unit leave SMs idle in the last wave (or all along, with fewer tiles
+    // than units); stream-K deals the K blocks out evenly instead.  It pays when that loss is
+    // noticeable and every unit still gets a few K blocks.
+    const long long num_kb = (p.K + BK - 1) / BK;
+    const long long waves = (args.total_tiles + units - 1) / units;
+    const double busy = static_cast<double>(args.total_tiles) / static_cast<double>(waves * units);
+    // (a fix-up costs about as much as a few K blocks: only long-K tiles are worth cutting)
+    const bool sk_worth = num_kb >= 64 && args.total_tiles * num_kb / units >= 32;
+    const bool sk_possible = args.total_tiles > 0 && args.total_tiles * num_kb / units >= 4 &&
+                             args.total_tiles * num_kb < 0x7FFFFFFFLL &&
+                             args.total_tiles / units + 2 <= kMaxSegments;
+    bool streamk = streamk_opt > 0 ? sk_possible : (streamk_opt < 0 && sk_possible && sk_worth && busy < 0.93);
+    if (streamk) {
+        int rc = streamk_workspace(p.device, p.stream, &args.sk_partials, &args.sk_flags, &args.sk_epoch);
+        if (rc != TTB_OK) streamk = false;  // no workspace for this stream: whole tiles
+    }
+    args.streamk = streamk ? 1 : 0;
+    if (!streamk && units > args.total_tiles) units = args.total_tiles;
     cfg.gridDim = dim3(static_cast<unsigned>(units * CG));
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_f32_3xtf32_kernel launch");
@@ -942,8 +1089,8 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
     args.dbg = opt.dbg;
     int sms = 148;
     sm_count(p.device, &sms);
-    if (opt.two_cta) return launch_cg<2>(p, args, sms);
-    return launch_cg<1>(p, args, sms);
+    if (opt.two_cta) return launch_cg<2>(p, args, sms, opt.streamk);
+    return launch_cg<1>(p, args, sms, opt.streamk);
 }
 
 }  // namespace ttb

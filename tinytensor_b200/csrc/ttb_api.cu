@@ -30,6 +30,7 @@ struct Options {
     int k_chunk = 0;
     int splitk = 1;
     int two_cta = -1;  // -1 = choose by shape
+    int streamk = -1;  // -1 = when whole tiles would leave SMs idle, 0 = never, 1 = whenever possible
     int mask_big = 0;
     int tc_profile = 0;
     int tc_debug = 0;
@@ -37,6 +38,13 @@ struct Options {
 Options g_opt;
 
 constexpr int kMaxDevices = 64;
+constexpr int kMaxStreamKSets = 8;
+struct StreamKSet {
+    cudaStream_t stream;
+    float *partials;
+    unsigned int *flags;
+    unsigned int epoch;
+};
 constexpr int kProfCtas = 256;
 constexpr size_t kProfBytes = kProfCtas * 8 * sizeof(long long);
 struct DeviceState {
@@ -46,6 +54,8 @@ struct DeviceState {
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
     long long *prof = nullptr;  // kProfCtas x 8 wait-cycle counters of the tcgen05 kernel
+    StreamKSet sk[kMaxStreamKSets];
+    int sk_count = 0;
     void *stage[3] = {nullptr, nullptr, nullptr};
     size_t stage_bytes[3] = {0, 0, 0};
 };
@@ -131,6 +141,48 @@ int sm_count(int device, int *out) {
     int rc = device_state(device, &d);
     if (rc != TTB_OK) return rc;
     *out = d->sms;
+    return TTB_OK;
+}
+
+// Stream-K workspace of the f32 tensor-core kernel: partial-sum slots and ready flags, one
+// set per (device, stream) so that launches on different streams never share one.  The
+// flags carry the launch number, so nothing has to be cleared between launches.
+int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags,
+                      unsigned int *epoch) {
+    DeviceState *d;
+    int rc = device_state(device, &d);
+    if (rc != TTB_OK) return rc;
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (int i = 0; i < d->sk_count; ++i) {
+        if (d->sk[i].stream == stream) {
+            *partials = d->sk[i].partials;
+            *flags = d->sk[i].flags;
+            *epoch = ++d->sk[i].epoch;
+            return TTB_OK;
+        }
+    }
+    if (d->sk_count == kMaxStreamKSets) {
+        set_error("stream-K workspaces for %d streams are in use on device %d", kMaxStreamKSets, device);
+        return TTB_ELIMIT;
+    }
+    StreamKSet s{};
+    s.stream = stream;
+    // One 32 x 128 fp32 slot per epilogue warp: at most 8 warps per SM's CTA.
+    const size_t slots = static_cast<size_t>(d->sms) * 8;
+    cudaError_t e = cudaMalloc(&s.partials, slots * 32 * 128 * sizeof(float));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(stream-K partials)");
+    e = cudaMalloc(&s.flags, slots * sizeof(unsigned int));
+    if (e != cudaSuccess) {
+        cudaFree(s.partials);
+        return cuda_fail(e, "cudaMalloc(stream-K flags)");
+    }
+    e = cudaMemset(s.flags, 0, slots * sizeof(unsigned int));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(stream-K flags)");
+    s.epoch = 1;
+    d->sk[d->sk_count++] = s;
+    *partials = s.partials;
+    *flags = s.flags;
+    *epoch = 1;
     return TTB_OK;
 }
 
@@ -276,6 +328,7 @@ static F32Options f32_options(bool two_cta) {
     o.two_cta = two_cta ? 1 : 0;
     o.mask_big = g_opt.mask_big;
     o.dbg = g_opt.tc_debug;
+    o.streamk = g_opt.streamk;
     return o;
 }
 
@@ -542,6 +595,14 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         g_opt.tc_profile = value != 0;
         return TTB_OK;
     }
+    if (!strcmp(key, "streamk")) {
+        if (value < -1 || value > 1) {
+            set_error("streamk must be -1 (automatic), 0 or 1");
+            return TTB_EINVAL;
+        }
+        g_opt.streamk = static_cast<int>(value);
+        return TTB_OK;
+    }
     if (!strcmp(key, "tc_debug")) {
         g_opt.tc_debug = static_cast<int>(value);
         return TTB_OK;
@@ -559,6 +620,7 @@ TTB_API int64_t ttb_get_option(const char *key) {
     if (!strcmp(key, "two_cta")) return g_opt.two_cta;
     if (!strcmp(key, "mask_big")) return g_opt.mask_big;
     if (!strcmp(key, "tc_profile")) return g_opt.tc_profile;
+    if (!strcmp(key, "streamk")) return g_opt.streamk;
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
