@@ -203,6 +203,35 @@ def test_host_buffer_entry_point(ttb, oracle):
         check(got, a, b)
 
 
+def test_host_buffer_pipeline_columns(ttb):
+    """Products large enough to be pipelined in column blocks through the host-buffer entry
+    point agree with the device-resident call: integers bit for bit, f32 within the rounding of
+    a different summation order.  rhs is a view into a wider matrix (row pitch > M)."""
+    rng = np.random.default_rng(28)
+    for dt, (N, K, M) in ((np.int32, (2048, 2048, 5000)), (np.float32, (2048, 4096, 4200))):
+        a, wide = random_operands(rng, dt, 1, N, K, M + 72, -8, 9)
+        b = wide[:, :, 8:8 + M]
+        got = ttb.batched_matmul_host(a, b)
+        want = host(ttb.batched_matmul(dev(a), dev(np.ascontiguousarray(b))))
+        if dt == np.int32:
+            assert np.array_equal(got, want)
+        else:
+            assert rel_to_max(got, want) <= 2e-6
+
+
+def test_host_buffer_pipeline_batches(ttb):
+    """Batched products large enough to be pipelined in groups of batches."""
+    rng = np.random.default_rng(29)
+    for dt, (B, N, K, M) in ((np.int32, (9, 1024, 2048, 1536)), (np.float32, (6, 2048, 2048, 1024))):
+        a, b = random_operands(rng, dt, B, N, K, M, -8, 9)
+        got = ttb.batched_matmul_host(a, b)
+        want = host(ttb.batched_matmul(dev(a), dev(b)))
+        if dt == np.int32:
+            assert np.array_equal(got, want)
+        else:
+            assert rel_to_max(got, want) <= 2e-6
+
+
 def test_multi_device_placement(ttb):
     """tests/test_multi_device_cuda.cpp:18-51: same-device work on device 1, cross-device throws."""
     if torch.cuda.device_count() < 2:

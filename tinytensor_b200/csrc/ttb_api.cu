@@ -39,6 +39,7 @@ Options g_opt;
 
 constexpr int kMaxDevices = 64;
 constexpr int kMaxStreamKSets = 8;
+constexpr int kHostChunks = 8;  // pipeline depth of the host-buffer entry point
 struct StreamKSet {
     cudaStream_t stream;
     float *partials;
@@ -57,6 +58,9 @@ struct DeviceState {
     StreamKSet sk[kMaxStreamKSets];
     int sk_count = 0;
     void *stage[3] = {nullptr, nullptr, nullptr};
+    cudaStream_t hs[3] = {nullptr, nullptr, nullptr};  // host-buffer entry point: upload, product, download
+    cudaEvent_t hev[2 * kHostChunks] = {};
+    bool hs_init = false;
     size_t stage_bytes[3] = {0, 0, 0};
 };
 DeviceState g_dev[kMaxDevices];
@@ -217,6 +221,22 @@ static int stage_get(DeviceState *d, int which, size_t bytes, void **out) {
         d->stage_bytes[which] = bytes;
     }
     *out = d->stage[which];
+    return TTB_OK;
+}
+
+// Streams and events of the host-buffer entry point's pipeline (created once per device).
+static int host_streams(DeviceState *d) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (d->hs_init) return TTB_OK;
+    for (int i = 0; i < 3; ++i) {
+        cudaError_t e = cudaStreamCreateWithFlags(&d->hs[i], cudaStreamNonBlocking);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreateWithFlags");
+    }
+    for (int i = 0; i < 2 * kHostChunks; ++i) {
+        cudaError_t e = cudaEventCreateWithFlags(&d->hev[i], cudaEventDisableTiming);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreateWithFlags");
+    }
+    d->hs_init = true;
     return TTB_OK;
 }
 
@@ -482,13 +502,105 @@ TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, vo
     }
     // Only the span each view touches travels; strides are kept, so the device
     // side consumes the same (possibly permuted) view.
-    e = cudaMemcpyAsync(da, p.a, a_bytes, cudaMemcpyHostToDevice, nullptr);
-    if (e != cudaSuccess) return cuda_fail(e, "H2D lhs");
-    e = cudaMemcpyAsync(db, p.b, b_bytes, cudaMemcpyHostToDevice, nullptr);
-    if (e != cudaSuccess) return cuda_fail(e, "H2D rhs");
+    const char *ha = static_cast<const char *>(p.a), *hb = static_cast<const char *>(p.b);
     p.a = da;
     p.b = db;
     p.c = dc;
+
+    // Large products are pipelined in chunks so that the upload of chunk j+1, the product of
+    // chunk j and the download of chunk j-1 overlap (PCIe is full duplex, the copy engines
+    // run beside the SMs):
+    //  * B == 1, rhs rows contiguous: chunks of output columns.  lhs goes up first, then the
+    //    column blocks of rhs (2-D copies); each block's product is written into its columns
+    //    of C and downloaded as soon as it is done.
+    //  * B >= 4, batch-major operands: chunks of batches.
+    // Anything else, and small products, take the plain path: copy, multiply, copy.
+    const double work = 2.0 * static_cast<double>(p.B) * p.N * p.K * p.M;
+    const int64_t a_one = (lhs->size[1] - 1) * lhs->stride[1] + (lhs->size[2] - 1) * lhs->stride[2] + 1;
+    const int64_t b_one = (rhs->size[1] - 1) * rhs->stride[1] + (rhs->size[2] - 1) * rhs->stride[2] + 1;
+    const bool by_cols = p.B == 1 && rhs->stride[2] == 1 && rhs->stride[1] >= p.M && p.M >= 1024 && work >= 4e10;
+    const bool by_batch = !by_cols && p.B >= 4 && lhs->stride[0] >= a_one && rhs->stride[0] >= b_one &&
+                          work >= 4e10;
+    if (by_cols || by_batch) {
+        rc = host_streams(d);
+        if (rc != TTB_OK) return rc;
+        cudaStream_t s_up = d->hs[0], s_mm = d->hs[1], s_down = d->hs[2];
+        const int64_t extent = by_cols ? p.M : p.B;
+        int nch = by_cols ? static_cast<int>(extent / 1024) : static_cast<int>(extent / 2);
+        if (nch > kHostChunks) nch = kHostChunks;
+        if (nch < 2) nch = 2;
+        // chunk edges: multiples of 128 columns / whole batches
+        const int64_t gran = by_cols ? 128 : 1;
+        const int64_t per = ((extent + nch - 1) / nch + gran - 1) / gran * gran;
+        if (by_cols) {
+            e = cudaMemcpyAsync(da, ha, a_bytes, cudaMemcpyHostToDevice, s_up);
+            if (e != cudaSuccess) return cuda_fail(e, "H2D lhs");
+        }
+        const Problem full = p;
+        for (int c = 0; c < nch; ++c) {
+            const int64_t x0 = c * per, x1 = (x0 + per < extent) ? x0 + per : extent;
+            if (x0 >= extent) break;
+            Problem q = full;
+            q.stream = s_mm;
+            if (by_cols) {
+                const size_t pitch = static_cast<size_t>(rhs->stride[1]) * es;
+                e = cudaMemcpy2DAsync(static_cast<char *>(db) + x0 * es, pitch, hb + x0 * es, pitch,
+                                      static_cast<size_t>(x1 - x0) * es, static_cast<size_t>(p.K),
+                                      cudaMemcpyHostToDevice, s_up);
+                if (e != cudaSuccess) return cuda_fail(e, "H2D rhs block");
+                q.b = static_cast<char *>(db) + x0 * es;
+                q.c = static_cast<char *>(dc) + x0 * es;
+                q.M = x1 - x0;
+            } else {
+                const size_t a_off = static_cast<size_t>(x0 * lhs->stride[0]) * es;
+                const size_t b_off = static_cast<size_t>(x0 * rhs->stride[0]) * es;
+                const size_t a_len = static_cast<size_t>((x1 - x0 - 1) * lhs->stride[0] + a_one) * es;
+                const size_t b_len = static_cast<size_t>((x1 - x0 - 1) * rhs->stride[0] + b_one) * es;
+                e = cudaMemcpyAsync(static_cast<char *>(da) + a_off, ha + a_off, a_len, cudaMemcpyHostToDevice, s_up);
+                if (e != cudaSuccess) return cuda_fail(e, "H2D lhs batches");
+                e = cudaMemcpyAsync(static_cast<char *>(db) + b_off, hb + b_off, b_len, cudaMemcpyHostToDevice, s_up);
+                if (e != cudaSuccess) return cuda_fail(e, "H2D rhs batches");
+                q.a = static_cast<char *>(da) + a_off;
+                q.b = static_cast<char *>(db) + b_off;
+                q.c = static_cast<char *>(dc) + static_cast<size_t>(x0) * p.N * p.M * es;
+                q.B = x1 - x0;
+            }
+            e = cudaEventRecord(d->hev[2 * c], s_up);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
+            e = cudaStreamWaitEvent(s_mm, d->hev[2 * c], 0);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
+            rc = dispatch(q);
+            if (rc != TTB_OK) {
+                cudaDeviceSynchronize();
+                return rc;
+            }
+            e = cudaEventRecord(d->hev[2 * c + 1], s_mm);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
+            e = cudaStreamWaitEvent(s_down, d->hev[2 * c + 1], 0);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
+            if (by_cols) {
+                const size_t pitch = static_cast<size_t>(p.M) * es;
+                e = cudaMemcpy2DAsync(static_cast<char *>(out) + x0 * es, pitch, static_cast<char *>(dc) + x0 * es, pitch,
+                                      static_cast<size_t>(x1 - x0) * es, static_cast<size_t>(p.N),
+                                      cudaMemcpyDeviceToHost, s_down);
+            } else {
+                const size_t off = static_cast<size_t>(x0) * p.N * p.M * es;
+                e = cudaMemcpyAsync(static_cast<char *>(out) + off, static_cast<char *>(dc) + off,
+                                    static_cast<size_t>(x1 - x0) * p.N * p.M * es, cudaMemcpyDeviceToHost, s_down);
+            }
+            if (e != cudaSuccess) return cuda_fail(e, "D2H out block");
+        }
+        for (int i = 0; i < 3; ++i) {
+            e = cudaStreamSynchronize(d->hs[i]);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+        }
+        return TTB_OK;
+    }
+
+    e = cudaMemcpyAsync(da, ha, a_bytes, cudaMemcpyHostToDevice, nullptr);
+    if (e != cudaSuccess) return cuda_fail(e, "H2D lhs");
+    e = cudaMemcpyAsync(db, hb, b_bytes, cudaMemcpyHostToDevice, nullptr);
+    if (e != cudaSuccess) return cuda_fail(e, "H2D rhs");
     rc = dispatch(p);
     if (rc != TTB_OK) return rc;
     e = cudaMemcpyAsync(out, dc, c_bytes, cudaMemcpyDeviceToHost, nullptr);
