@@ -104,6 +104,35 @@ TTB_API int ttb_batched_matmul_strided_out(const ttb_view *lhs, const ttb_view *
                                            const int64_t out_stride[3], int dtype,
                                            int device_id, void *stream);
 
+/* Activations of the fused form below. */
+enum ttb_activation {
+    TTB_ACT_NONE = 0,
+    TTB_ACT_RELU = 1   /* max(x, 0) as the reference's OpReLU (backend/common/kernel/unary.hpp:403-407):
+                          NaN and -0.0 pass through; floating-point dtypes only, as there */
+};
+
+/* Product with a fused epilogue: out = act(lhs . rhs + addend), written to the
+ * strided destination like ttb_batched_matmul_strided_out.  `addend` (NULL = none)
+ * is a [B,N,M] view of the same dtype; any of its strides may be 0, so it can be
+ *   - a bias over output columns, stride {0,0,1}: tinytensor's Linear,
+ *     `matmul(x, w) + bias.expand(...)` (nn/linear.cpp:45-48), in one kernel instead
+ *     of a matmul, an expand and a binary add kernel;
+ *   - a bias over output rows, stride {0,1,0}: the per-channel bias of conv2d's
+ *     GEMM (backend/cuda/conv.cu:149-183);
+ *   - the destination itself (same pointer, offset and strides): accumulation
+ *     out += lhs . rhs, what backward's add_grad does with a second kernel
+ *     (tensor/tensor.cpp:1137-1160).  Each element is read and written by the
+ *     same thread, so this in-place form is safe; any other overlap of `addend`
+ *     with `out` is not.
+ * Integers wrap exactly as a separate add in T would; for floats the addend is
+ * added to the fp32 / fp64 sum before the one rounding of the store.
+ * `activation` is a ttb_activation; TTB_ACT_RELU needs a floating-point dtype
+ * (the reference's relu on integers yields floats, backend/common/unary.h:187). */
+TTB_API int ttb_batched_matmul_fused(const ttb_view *lhs, const ttb_view *rhs, void *out,
+                                     int64_t out_offset, const int64_t out_stride[3],
+                                     const ttb_view *addend, int activation, int dtype,
+                                     int device_id, void *stream);
+
 /* Product fused with an all-gather of the result over NVLink (f32, tensor-core
  * kernel only).  Computes lhs . rhs into the strided destination `out` on this GPU
  * like ttb_batched_matmul_strided_out, and stores every finished tile into the
@@ -162,6 +191,39 @@ TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, vo
 TTB_API int ttb_batched_matmul_static_scratch(const ttb_view *lhs, const ttb_view *rhs,
                                               void *out, int dtype, int device_id,
                                               void *stream);
+
+/* ---- conv2d on the matmul path -------------------------------------------
+ *
+ * The other caller of the reference's matmul kernel: conv2d forward and backward
+ * (backend/cuda/conv.cu:37-197 and :199-403) unroll one batch item at a time and run
+ * matmul_kernel<T> on it.  These two entry points replace
+ * tinytensor::cuda::batched_conv2d_forward_runner / batched_conv2d_backward_runner
+ * (backend/cuda/conv.h:16-30): the whole batch is unrolled by one kernel and each
+ * product is one batched matmul through the same dispatch as ttb_batched_matmul
+ * (bias fused into the forward product's epilogue).
+ *
+ * Tensors are contiguous, as the reference requires (it calls contiguous() on the
+ * input, conv.cu:77): input [batch, c_in, h_in, w_in], weight [c_out, c_in, kernel,
+ * kernel], bias [c_out] or NULL, out / grad_out [batch, c_out, h_out, w_out] with
+ * h_out = (h_in + 2*padding - kernel) / stride + 1 (likewise w_out).  All device
+ * pointers to the first element, one dtype (any but bool8).  Integers wrap like the
+ * reference's; f32 / f64 meet the matmul tolerances.  The unrolled columns live in a
+ * cached workspace (at most 2 GiB; larger batches are processed in groups of batch
+ * items).  Neither call synchronises. */
+typedef struct ttb_conv2d_desc {
+    int64_t batch, c_in, h_in, w_in;
+    int64_t c_out, kernel, stride, padding;
+} ttb_conv2d_desc;
+
+TTB_API int ttb_conv2d_forward(const void *input, const void *weight, const void *bias, void *out,
+                               const ttb_conv2d_desc *desc, int dtype, int device_id, void *stream);
+
+/* grad_input [batch, c_in, h_in, w_in] and grad_weight [c_out, c_in, kernel, kernel] are
+ * overwritten; grad_bias [c_out] is written when not NULL (the reference returns it only
+ * when the forward had a bias, conv.cu:396-399). */
+TTB_API int ttb_conv2d_backward(const void *grad_out, const void *input, const void *weight,
+                                void *grad_input, void *grad_weight, void *grad_bias,
+                                const ttb_conv2d_desc *desc, int dtype, int device_id, void *stream);
 
 /* ---- multi-GPU partitioner (host logic only; no communication) ----------
  *

@@ -70,6 +70,76 @@ class Oracle:
         return out
 
 
+    # ---- conv2d (oracle/conv_oracle.c; the reference's kernels in oracle/_ref/libttref*.so)
+    @staticmethod
+    def _conv_dims(x, w, stride, padding):
+        B, C_in, H_in, W_in = x.shape
+        C_out, c2, K, k2 = w.shape
+        assert c2 == C_in and K == k2 and x.dtype == w.dtype
+        H_out = (H_in + 2 * padding - K) // stride + 1
+        W_out = (W_in + 2 * padding - K) // stride + 1
+        ints = [ctypes.c_int(v) for v in (B, C_in, H_in, W_in, C_out, K, stride, padding)]
+        return ints, (B, C_out, H_out, W_out)
+
+    def _conv_lib(self, which: str):
+        lib = {"port": self.port, "ref": self.ref, "ref_strict": self.ref_strict}[which]
+        assert lib is not None, f"oracle library '{which}' has not been built"
+        return lib, ("oracle" if which == "port" else "ref")
+
+    def conv2d_forward(self, x, w, bias=None, stride=1, padding=0, which="port"):
+        lib, prefix = self._conv_lib(which)
+        x, w = np.ascontiguousarray(x), np.ascontiguousarray(w)
+        ints, oshape = self._conv_dims(x, w, stride, padding)
+        y = np.empty(oshape, dtype=x.dtype)
+        bptr = None
+        if bias is not None:
+            bias = np.ascontiguousarray(bias)
+            bptr = ctypes.c_void_p(bias.ctypes.data)
+        fn = getattr(lib, f"{prefix}_conv2d_forward_{_NAMES[x.dtype]}")
+        fn(ctypes.c_void_p(x.ctypes.data), ctypes.c_void_p(w.ctypes.data), bptr, ctypes.c_void_p(y.ctypes.data), *ints)
+        return y
+
+    def conv2d_backward(self, g, x, w, stride=1, padding=0, which="port", with_bias=True):
+        """-> (grad_input, grad_weight, grad_bias or None).  The reference libraries return no
+        bias gradient (the reference computes it with tensor reductions outside the runner's
+        kernels, backend/cpu/conv.cpp:283)."""
+        lib, prefix = self._conv_lib(which)
+        g, x, w = np.ascontiguousarray(g), np.ascontiguousarray(x), np.ascontiguousarray(w)
+        ints, oshape = self._conv_dims(x, w, stride, padding)
+        assert g.shape == oshape and g.dtype == x.dtype
+        gx, gw = np.empty_like(x), np.empty_like(w)
+        fn = getattr(lib, f"{prefix}_conv2d_backward_{_NAMES[x.dtype]}")
+        if which == "port":
+            gb = np.empty(w.shape[0], dtype=x.dtype) if with_bias else None
+            fn(ctypes.c_void_p(g.ctypes.data), ctypes.c_void_p(x.ctypes.data), ctypes.c_void_p(w.ctypes.data),
+               ctypes.c_void_p(gx.ctypes.data), ctypes.c_void_p(gw.ctypes.data),
+               ctypes.c_void_p(gb.ctypes.data) if gb is not None else None, *ints)
+            return gx, gw, gb
+        fn(ctypes.c_void_p(g.ctypes.data), ctypes.c_void_p(x.ctypes.data), ctypes.c_void_p(w.ctypes.data),
+           ctypes.c_void_p(gx.ctypes.data), ctypes.c_void_p(gw.ctypes.data), *ints)
+        return gx, gw, None
+
+
+def conv2d_direct(x: np.ndarray, w: np.ndarray, stride: int, padding: int) -> np.ndarray:
+    """The direct definition the reference's test uses as its expected value
+    (tests/test_conv.cpp:28-73): Y[b,m,h,w] += T(X * W) over c, p, q, accumulated in T.
+    Integers wrap (computed mod 2^64, truncated); floats are summed in float64."""
+    B, C_in, H_in, W_in = x.shape
+    C_out, _, K, _ = w.shape
+    H_out = (H_in + 2 * padding - K) // stride + 1
+    W_out = (W_in + 2 * padding - K) // stride + 1
+    wide = np.uint64 if x.dtype.kind in "iu" else np.float64
+    xp = np.zeros((B, C_in, H_in + 2 * padding, W_in + 2 * padding), dtype=wide)
+    xp[:, :, padding:padding + H_in, padding:padding + W_in] = x.astype(wide)
+    y = np.zeros((B, C_out, H_out, W_out), dtype=wide)
+    ww = w.astype(wide)
+    for p in range(K):
+        for q in range(K):
+            patch = xp[:, :, p:p + stride * (H_out - 1) + 1:stride, q:q + stride * (W_out - 1) + 1:stride]
+            y += np.einsum("bchw,mc->bmhw", patch, ww[:, :, p, q])
+    return y.astype(x.dtype) if x.dtype.kind in "iu" else y
+
+
 class RefCuda:
     """The reference's own CUDA matmul kernel (oracle/_ref/libttref_cuda.so), launched the way
     its runner launches it: contiguous operands, default stream."""

@@ -11,9 +11,14 @@ There is no CPU or eager fallback: importing works without the library, but any
 compute call raises if ``libttb.so`` is missing.
 """
 from .backend import (  # noqa: F401
+    Activation,
     TTBError,
     Variant,
     batched_matmul,
+    batched_matmul_fused,
+    conv2d,
+    conv2d_backward,
+    linear,
     batched_matmul_host,
     batched_matmul_static_scratch,
     check_device,
@@ -31,7 +36,7 @@ from .backend import (  # noqa: F401
 from .partition import Partition, ShardedMatmul, partition  # noqa: F401
 
 __all__ = [
-    "TTBError", "Variant", "batched_matmul", "batched_matmul_host", "batched_matmul_static_scratch",
+    "Activation", "TTBError", "Variant", "batched_matmul", "batched_matmul_fused", "conv2d", "conv2d_backward", "linear", "batched_matmul_host", "batched_matmul_static_scratch",
     "check_device", "get_option",
     "last_variant", "launch_count", "lib", "lib_path", "matmul", "matmul_allgather", "set_option", "tma_eligible",
     "view_of", "Partition", "ShardedMatmul", "partition",

@@ -98,6 +98,16 @@ def lib() -> ctypes.CDLL:
         ctypes.c_void_p,
     ]
     L.ttb_batched_matmul_strided_out.restype = ctypes.c_int
+    L.ttb_batched_matmul_fused.argtypes = [
+        vp, vp, ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64), vp, ctypes.c_int, ctypes.c_int,
+        ctypes.c_int, ctypes.c_void_p]
+    L.ttb_batched_matmul_fused.restype = ctypes.c_int
+    L.ttb_conv2d_forward.argtypes = [ctypes.c_void_p] * 4 + [ctypes.POINTER(_ConvDesc), ctypes.c_int, ctypes.c_int,
+                                     ctypes.c_void_p]
+    L.ttb_conv2d_forward.restype = ctypes.c_int
+    L.ttb_conv2d_backward.argtypes = [ctypes.c_void_p] * 6 + [ctypes.POINTER(_ConvDesc), ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_void_p]
+    L.ttb_conv2d_backward.restype = ctypes.c_int
     L.ttb_matmul_allgather.argtypes = [
         vp, vp, ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_void_p),
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
@@ -233,6 +243,131 @@ def batched_matmul(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor | Non
     if rc != 0:
         _raise(rc)
     return out
+
+
+class Activation(enum.IntEnum):
+    NONE = 0
+    RELU = 1
+
+
+def batched_matmul_fused(lhs: torch.Tensor, rhs: torch.Tensor, addend: torch.Tensor | None = None,
+                         activation: Activation = Activation.NONE, out: torch.Tensor | None = None,
+                         stream=None) -> torch.Tensor:
+    """``ttb_batched_matmul_fused``: act(lhs . rhs + addend) in one kernel.
+
+    `addend` is anything that expands to the result shape [B,N,M] without a copy: a bias over
+    columns ([M]), over rows ([N,1]), a full tensor, or `out` itself (accumulation,
+    out += lhs . rhs).  Replaces the reference's matmul + expand + add (nn/linear.cpp:45-48),
+    conv2d's per-image bias add (backend/cuda/conv.cu:163-183) and add_grad's second kernel
+    (tensor/tensor.cpp:1137-1160)."""
+    if lhs.dim() != 3 or rhs.dim() != 3 or lhs.dtype != rhs.dtype or lhs.device != rhs.device:
+        raise TTBError("operands must be rank-3 tensors of one dtype on one device")
+    if lhs.device.type != "cuda":
+        raise TTBError("tinytensor_b200 only runs on CUDA devices (no CPU fallback)")
+    if lhs.dtype not in _DTYPE_CODE:
+        raise TTBError(f"unsupported dtype {lhs.dtype}")
+    shape = (lhs.shape[0], lhs.shape[1], rhs.shape[2])
+    dev = lhs.device.index if lhs.device.index is not None else torch.cuda.current_device()
+    if out is None:
+        if lhs.shape[0] != rhs.shape[0] or lhs.shape[2] != rhs.shape[1]:
+            raise TTBError(f"shapes {tuple(lhs.shape)} and {tuple(rhs.shape)} do not multiply")
+        with torch.cuda.device(dev):
+            out = torch.empty(shape, dtype=lhs.dtype, device=lhs.device)
+    elif tuple(out.shape) != shape or out.dtype != lhs.dtype or out.device != lhs.device:
+        raise TTBError(f"out must be a {shape} tensor of the operands' dtype and device")
+    av = None
+    if addend is not None:
+        if addend.dtype != lhs.dtype or addend.device != lhs.device:
+            raise TTBError("addend must have the operands' dtype and device")
+        try:
+            av = view_of(addend.expand(shape))
+        except RuntimeError as e:
+            raise TTBError(f"addend of shape {tuple(addend.shape)} does not expand to {shape}") from e
+    lv, rv = view_of(lhs), view_of(rhs)
+    strides = (ctypes.c_int64 * 3)(*out.stride())
+    rc = lib().ttb_batched_matmul_fused(
+        ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.untyped_storage().data_ptr()), out.storage_offset(),
+        strides, ctypes.byref(av) if av is not None else None, int(activation), _DTYPE_CODE[lhs.dtype], dev,
+        ctypes.c_void_p(_stream_ptr(stream)))
+    if rc != 0:
+        _raise(rc)
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           activation: Activation = Activation.NONE) -> torch.Tensor:
+    """tinytensor's Linear.forward (nn/linear.cpp:41-50): x[..., in] . weight[in, out] + bias[out],
+    as one fused kernel (the reference runs matmul, expand and a binary add)."""
+    if weight.dim() != 2 or x.shape[-1] != weight.shape[0]:
+        raise TTBError(f"linear: x[..., {x.shape[-1]}] does not match weight {tuple(weight.shape)}")
+    x2 = x.reshape(1, -1, x.shape[-1])
+    out = batched_matmul_fused(x2, weight.unsqueeze(0), bias, activation)
+    return out.reshape(*x.shape[:-1], weight.shape[1])
+
+
+class _ConvDesc(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int64) for n in ("batch", "c_in", "h_in", "w_in", "c_out", "kernel", "stride", "padding")]
+
+
+def _conv_desc(input: torch.Tensor, weight: torch.Tensor, stride: int, padding: int):
+    if input.dim() != 4 or weight.dim() != 4:
+        raise TTBError(f"conv2d expects rank-4 input and weight, got {input.dim()} and {weight.dim()}")
+    if input.shape[1] != weight.shape[1] or weight.shape[2] != weight.shape[3]:
+        raise TTBError(f"conv2d: input {tuple(input.shape)} does not match weight {tuple(weight.shape)} "
+                       "(channels must agree, kernels are square)")
+    if input.dtype != weight.dtype or input.device != weight.device or input.device.type != "cuda":
+        raise TTBError("conv2d: input and weight must share a dtype and a CUDA device")
+    if input.dtype not in _DTYPE_CODE:
+        raise TTBError(f"unsupported dtype {input.dtype}")
+    B, C_in, H_in, W_in = input.shape
+    d = _ConvDesc(B, C_in, H_in, W_in, weight.shape[0], weight.shape[2], int(stride), int(padding))
+    h_out = (H_in + 2 * padding - weight.shape[2]) // stride + 1 if stride > 0 else 0
+    w_out = (W_in + 2 * padding - weight.shape[2]) // stride + 1 if stride > 0 else 0
+    return d, (B, weight.shape[0], h_out, w_out)
+
+
+def conv2d(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, stride: int = 1,
+           padding: int = 0, stream=None) -> torch.Tensor:
+    """tinytensor's conv2d forward (backend/cuda/conv.cu:37-197) through ``ttb_conv2d_forward``:
+    input [B,C_in,H,W], weight [C_out,C_in,K,K], bias [C_out] -> [B,C_out,H_out,W_out]."""
+    d, oshape = _conv_desc(input, weight, stride, padding)
+    input, weight = input.contiguous(), weight.contiguous()  # conv.cu:77
+    if bias is not None:
+        if bias.shape != (weight.shape[0],) or bias.dtype != input.dtype or bias.device != input.device:
+            raise TTBError("conv2d: bias must be [C_out] of the input's dtype and device")
+        bias = bias.contiguous()
+    dev = input.device.index if input.device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(dev):
+        out = torch.empty([max(v, 0) for v in oshape], dtype=input.dtype, device=input.device)
+    rc = lib().ttb_conv2d_forward(ctypes.c_void_p(input.data_ptr()), ctypes.c_void_p(weight.data_ptr()),
+                                  ctypes.c_void_p(bias.data_ptr()) if bias is not None else None,
+                                  ctypes.c_void_p(out.data_ptr()), ctypes.byref(d), _DTYPE_CODE[input.dtype], dev,
+                                  ctypes.c_void_p(_stream_ptr(stream)))
+    if rc != 0:
+        _raise(rc)
+    return out
+
+
+def conv2d_backward(grad_output: torch.Tensor, input: torch.Tensor, weight: torch.Tensor, stride: int = 1,
+                    padding: int = 0, with_bias: bool = True, stream=None):
+    """conv2d backward (backend/cuda/conv.cu:199-403) through ``ttb_conv2d_backward``:
+    -> (grad_input, grad_weight, grad_bias or None)."""
+    d, oshape = _conv_desc(input, weight, stride, padding)
+    if tuple(grad_output.shape) != tuple(oshape) or grad_output.dtype != input.dtype or grad_output.device != input.device:
+        raise TTBError(f"conv2d backward: grad_output must be {tuple(oshape)} of the input's dtype and device")
+    grad_output, input, weight = grad_output.contiguous(), input.contiguous(), weight.contiguous()
+    dev = input.device.index if input.device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(dev):
+        gx, gw = torch.empty_like(input), torch.empty_like(weight)
+        gb = torch.empty(weight.shape[0], dtype=input.dtype, device=input.device) if with_bias else None
+    rc = lib().ttb_conv2d_backward(ctypes.c_void_p(grad_output.data_ptr()), ctypes.c_void_p(input.data_ptr()),
+                                   ctypes.c_void_p(weight.data_ptr()), ctypes.c_void_p(gx.data_ptr()),
+                                   ctypes.c_void_p(gw.data_ptr()),
+                                   ctypes.c_void_p(gb.data_ptr()) if gb is not None else None, ctypes.byref(d),
+                                   _DTYPE_CODE[input.dtype], dev, ctypes.c_void_p(_stream_ptr(stream)))
+    if rc != 0:
+        _raise(rc)
+    return gx, gw, gb
 
 
 def matmul_allgather(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor, peer_bases, stream=None) -> torch.Tensor:

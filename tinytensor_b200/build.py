@@ -35,6 +35,7 @@ SOURCES = [
     "gemm_simt.cu",
     "gemm_f32_tcgen05.cu",
     "gemm_f64_dmma.cu",
+    "conv2d.cu",
 ]
 
 
@@ -88,23 +89,26 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
-def compile_check_shim(reference_root: Path, export_header_dir: Path) -> Path:
-    """Compiles csrc/tt_runner_shim.cu (the tinytensor-side adapter) to an object against
-    tinytensor's headers, the way tinytensor's own CUDA backend is compiled (C++20,
-    --expt-relaxed-constexpr, TT_CUDA).  `export_header_dir` holds a tt/export.h (the file
-    tinytensor's CMake generates)."""
+def compile_check_shim(reference_root: Path, export_header_dir: Path) -> list[Path]:
+    """Compiles the tinytensor-side adapters (csrc/tt_runner_shim.cu for matmul,
+    csrc/tt_conv_shim.cu for conv2d) to objects against tinytensor's headers, the way
+    tinytensor's own CUDA backend is compiled (C++20, --expt-relaxed-constexpr, TT_CUDA).
+    `export_header_dir` holds a tt/export.h (the file tinytensor's CMake generates)."""
     OBJ.mkdir(exist_ok=True)
-    obj = OBJ / "tt_runner_shim.o"
-    cmd = [
-        _nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++20", "--expt-relaxed-constexpr",
-        "-DTT_CUDA", "-DTINYTENSOR_STATIC_DEFINE", "-O2", "-Xcompiler", "-fPIC",
-        f"-I{reference_root}/include", f"-I{reference_root}/tinytensor", f"-I{export_header_dir}",
-        "-c", str(CSRC / "tt_runner_shim.cu"), "-o", str(obj),
-    ]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"tt_runner_shim.cu does not compile against {reference_root}:\n{r.stdout}\n{r.stderr}")
-    return obj
+    objs = []
+    for name in ("tt_runner_shim", "tt_conv_shim"):
+        obj = OBJ / f"{name}.o"
+        cmd = [
+            _nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++20", "--expt-relaxed-constexpr",
+            "-DTT_CUDA", "-DTINYTENSOR_STATIC_DEFINE", "-O2", "-Xcompiler", "-fPIC",
+            f"-I{reference_root}/include", f"-I{reference_root}/tinytensor", f"-I{export_header_dir}",
+            "-c", str(CSRC / f"{name}.cu"), "-o", str(obj),
+        ]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"{name}.cu does not compile against {reference_root}:\n{r.stdout}\n{r.stderr}")
+        objs.append(obj)
+    return objs
 
 
 if __name__ == "__main__":

@@ -23,7 +23,21 @@ struct Problem {
     int dtype;
     int device;
     cudaStream_t stream;
+    // Fused epilogue: out = act(lhs.rhs + addend).  `addend` is a [B,N,M] view of the same dtype
+    // whose strides may be 0 (a bias row or column broadcast) or may describe `c` itself
+    // (accumulation into the output); nullptr = none.  Element pointer includes the offset.
+    const void *d = nullptr;
+    int64_t d_sb = 0, d_si = 0, d_sj = 0;
+    int act = 0;  // TTB_ACT_NONE / TTB_ACT_RELU
 };
+
+// The same, as the kernels take it.
+struct Epilogue {
+    const void *d;
+    long long d_sb, d_si, d_sj;
+    int act;
+};
+inline Epilogue epilogue_of(const Problem &p) { return Epilogue{p.d, p.d_sb, p.d_si, p.d_sj, p.act}; }
 
 // Error word written by kernels whose bounded waits gave up.  One per device,
 // in ordinary global memory owned by the library.

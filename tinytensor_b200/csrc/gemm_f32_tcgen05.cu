@@ -98,6 +98,9 @@ struct alignas(64) TcArgs {
     CUtensorMap tmap_b;
     float *c;
     long long c_sb, c_si, c_sj;
+    const float *d;  // fused epilogue: addend view (bias row / column, or C itself), nullptr = none
+    long long d_sb, d_si, d_sj;
+    int act;         // TTB_ACT_*
     int N, M, K, B;
     int a_mn_major, b_mn_major;
     int a_batch_mul, b_batch_mul;
@@ -635,6 +638,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         bool ok = true;
         const bool vec_ok = args.c_sj == 1 && (args.c_si & 3) == 0 && (args.c_sb & 3) == 0 &&
                             (reinterpret_cast<uintptr_t>(args.c) & 15) == 0;
+        const bool dvec_ok = args.d_sj == 1 && (args.d_si & 3) == 0 && (args.d_sb & 3) == 0 &&
+                             (reinterpret_cast<uintptr_t>(args.d) & 15) == 0;
         uint32_t acc_empty_remote[2] = {0, 0};
         if constexpr (PAIR) {
             for (int a = 0; a < 2; ++a) acc_empty_remote[a] = mapa(smem_u32(&acc_empty_bar[a]), 0);
@@ -746,6 +751,35 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             }
             if (row < args.N && col0 < args.M) {
                 float *crow = args.c + static_cast<long long>(b) * args.c_sb + static_cast<long long>(row) * args.c_si;
+                if (args.d != nullptr) {
+                    // Fused addend.  The thread that adds d[b,row,col] is the one that stores
+                    // c[b,row,col], so d may be C itself (accumulation).
+                    const float *drow =
+                        args.d + static_cast<long long>(b) * args.d_sb + static_cast<long long>(row) * args.d_si;
+                    if (args.d_sj == 0) {
+                        const float v = __ldg(drow);
+#pragma unroll
+                        for (int j = 0; j < 128; ++j) sum[j] += v;
+                    } else if (dvec_ok && col0 + 128 <= args.M) {
+                        const float4 *src = reinterpret_cast<const float4 *>(drow + col0);
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) {
+                            const float4 v = src[q];
+                            sum[4 * q] += v.x;
+                            sum[4 * q + 1] += v.y;
+                            sum[4 * q + 2] += v.z;
+                            sum[4 * q + 3] += v.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 128; ++j)
+                            if (col0 + j < args.M) sum[j] += drow[static_cast<long long>(col0 + j) * args.d_sj];
+                    }
+                }
+                if (args.act == TTB_ACT_RELU) {
+#pragma unroll
+                    for (int j = 0; j < 128; ++j) sum[j] = sum[j] < 0.0f ? 0.0f : sum[j];
+                }
                 if (vec_ok && col0 + 128 <= args.M) {
                     float4 *dst = reinterpret_cast<float4 *>(crow + col0);
 #pragma unroll
@@ -1067,6 +1101,11 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
     args.c_sb = p.c_sb;
     args.c_si = p.c_si;
     args.c_sj = p.c_sj;
+    args.d = static_cast<const float *>(p.d);
+    args.d_sb = p.d_sb;
+    args.d_si = p.d_si;
+    args.d_sj = p.d_sj;
+    args.act = p.act;
     args.N = static_cast<int>(p.N);
     args.M = static_cast<int>(p.M);
     args.K = static_cast<int>(p.K);

@@ -32,6 +32,7 @@ struct DmmaArgs {
     long long a_sb, a_si, a_sk;
     long long b_sb, b_sk, b_sj;
     long long c_sb, c_si, c_sj;
+    Epilogue ep;
 };
 
 __device__ __forceinline__ void dmma_m16n8k4(double (&c)[4], double a0, double a1, double b0) {
@@ -149,11 +150,23 @@ __global__ void __launch_bounds__(THREADS) gemm_f64_dmma_kernel(DmmaArgs p) {
                 const long long gj = n0 + wn + j * 8 + 2 * t;
                 if (gj >= p.M) continue;
                 double *dst = c + gi * p.c_si + gj * p.c_sj;
+                double v0 = acc[i][j][2 * h], v1 = acc[i][j][2 * h + 1];
+                if (p.ep.d) {
+                    // addend (bias row / column, or C itself): same thread reads, then writes
+                    const double *d = static_cast<const double *>(p.ep.d) + batch * p.ep.d_sb + gi * p.ep.d_si +
+                                      gj * p.ep.d_sj;
+                    v0 += d[0];
+                    if (gj + 1 < p.M) v1 += d[p.ep.d_sj];
+                }
+                if (p.ep.act == TTB_ACT_RELU) {
+                    v0 = v0 < 0.0 ? 0.0 : v0;
+                    v1 = v1 < 0.0 ? 0.0 : v1;
+                }
                 if (vec_ok && gj + 1 < p.M) {
-                    *reinterpret_cast<double2 *>(dst) = make_double2(acc[i][j][2 * h], acc[i][j][2 * h + 1]);
+                    *reinterpret_cast<double2 *>(dst) = make_double2(v0, v1);
                 } else {
-                    dst[0] = acc[i][j][2 * h];
-                    if (gj + 1 < p.M) dst[p.c_sj] = acc[i][j][2 * h + 1];
+                    dst[0] = v0;
+                    if (gj + 1 < p.M) dst[p.c_sj] = v1;
                 }
             }
         }
@@ -188,6 +201,7 @@ int launch_f64_dmma(const Problem &p) {
     a.c_sb = p.c_sb;
     a.c_si = p.c_si;
     a.c_sj = p.c_sj;
+    a.ep = epilogue_of(p);
     dim3 grid(static_cast<unsigned>((p.M + BN - 1) / BN), static_cast<unsigned>((p.N + BM - 1) / BM),
               static_cast<unsigned>(p.B));
     gemm_f64_dmma_kernel<<<grid, THREADS, 0, p.stream>>>(a);

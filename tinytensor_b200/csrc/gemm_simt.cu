@@ -87,7 +87,20 @@ struct SimtArgs {
     int splits;          // K is cut into `splits` ranges of k_per_split (grid.z = B * splits)
     long long k_per_split;
     long long c_ss;      // stride between split partials in c (split-K only)
+    Epilogue ep;         // applied by whoever writes the final value (not to split partials)
 };
+
+// acc (+ addend) -> T, then the activation.  Integer sums wrap: widening the addend and
+// narrowing once equals adding in T.  ReLU is std::max(x, 0): NaN and -0.0 pass through.
+template <typename T, typename A>
+__device__ __forceinline__ T finish(A acc, const Epilogue &ep, long long b, long long i, long long j) {
+    if (ep.d) acc = acc + widen<T>(static_cast<const T *>(ep.d)[b * ep.d_sb + i * ep.d_si + j * ep.d_sj]);
+    T r = narrow<T>(acc);
+    if constexpr (std::is_floating_point_v<T>) {
+        if (ep.act == TTB_ACT_RELU) r = r < T(0) ? T(0) : r;
+    }
+    return r;
+}
 
 template <typename T, int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN)) simt_gemm_kernel(SimtArgs p) {
@@ -246,7 +259,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) simt_gemm_kernel(SimtAr
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
             const long long gj = n0 + (j / HN) * (BN / 2) + tx * HN + (j % HN);
-            if (gj < p.M) c[gi * p.c_si + gj * p.c_sj] = narrow<T>(acc[i][j]);
+            if (gj < p.M) c[gi * p.c_si + gj * p.c_sj] = finish<T>(acc[i][j], p.ep, batch, gi, gj);
         }
     }
 }
@@ -254,7 +267,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) simt_gemm_kernel(SimtAr
 // Sums `splits` partials (each [B,N,M] contiguous, split-major) into the strided output.
 template <typename T>
 __global__ void splitk_reduce_kernel(const T *__restrict__ part, T *__restrict__ c, long long B, long long N,
-                                     long long M, int splits, long long c_sb, long long c_si, long long c_sj) {
+                                     long long M, int splits, long long c_sb, long long c_si, long long c_sj,
+                                     Epilogue ep) {
     using A = typename AccOf<T>::type;
     const long long total = B * N * M;
     for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -264,7 +278,7 @@ __global__ void splitk_reduce_kernel(const T *__restrict__ part, T *__restrict__
         const long long bb = idx / (N * M);
         const long long r = (idx / M) % N;
         const long long col = idx % M;
-        c[bb * c_sb + r * c_si + col * c_sj] = narrow<T>(s);
+        c[bb * c_sb + r * c_si + col * c_sj] = finish<T>(s, ep, bb, r, col);
     }
 }
 
@@ -291,6 +305,7 @@ int launch_tile(const Problem &p, int splits, void *scratch) {
         a.c_si = p.M;
         a.c_sj = 1;
         a.c_ss = p.B * p.N * p.M;
+        a.ep = Epilogue{nullptr, 0, 0, 0, 0};
     } else {
         a.k_per_split = p.K;
         a.c = p.c;
@@ -298,6 +313,7 @@ int launch_tile(const Problem &p, int splits, void *scratch) {
         a.c_si = p.c_si;
         a.c_sj = p.c_sj;
         a.c_ss = 0;
+        a.ep = epilogue_of(p);
     }
     const long long gx = (p.M + BN - 1) / BN, gy = (p.N + BM - 1) / BM, gz = p.B * splits;
     if (gy > 65535 || gz > 65535) {
@@ -313,7 +329,7 @@ int launch_tile(const Problem &p, int splits, void *scratch) {
         const int blocks = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
         splitk_reduce_kernel<T><<<blocks, 256, 0, p.stream>>>(static_cast<const T *>(scratch),
                                                               static_cast<T *>(p.c), p.B, p.N, p.M, splits,
-                                                              p.c_sb, p.c_si, p.c_sj);
+                                                              p.c_sb, p.c_si, p.c_sj, epilogue_of(p));
         e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(e, "splitk_reduce_kernel launch");
     }

@@ -34,11 +34,13 @@ struct Options {
     int mask_big = 0;
     int tc_profile = 0;
     int tc_debug = 0;
+    int conv_columns_mb = 2048;  // budget of conv2d's unrolled-columns workspace
 };
 Options g_opt;
 
 constexpr int kMaxDevices = 64;
 constexpr int kMaxStreamKSets = 8;
+constexpr int kExtraSlots = 3;
 constexpr int kHostChunks = 8;  // pipeline depth of the host-buffer entry point
 struct StreamKSet {
     cudaStream_t stream;
@@ -54,6 +56,8 @@ struct DeviceState {
     DeviceStatus *status = nullptr;
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
+    void *extra[kExtraSlots] = {};
+    size_t extra_bytes[kExtraSlots] = {};
     long long *prof = nullptr;  // kProfCtas x 8 wait-cycle counters of the tcgen05 kernel
     StreamKSet sk[kMaxStreamKSets];
     int sk_count = 0;
@@ -80,7 +84,7 @@ int cuda_fail(cudaError_t e, const char *what) {
 }
 
 void note_launch(int variant, int count) {
-    g_last_variant = variant;
+    if (variant >= 0) g_last_variant = variant;
     g_launches += count;
 }
 
@@ -139,6 +143,8 @@ long long *profile_ptr(int device) {
     if (device_state(device, &d) != TTB_OK) return nullptr;
     return d->prof;
 }
+
+size_t conv_columns_budget() { return static_cast<size_t>(g_opt.conv_columns_mb) << 20; }
 
 int sm_count(int device, int *out) {
     DeviceState *d;
@@ -208,6 +214,33 @@ int workspace_get(int device, size_t bytes, void **out) {
         d->workspace_bytes = want;
     }
     *out = d->workspace;
+    return TTB_OK;
+}
+
+// Further cached buffers, by slot (1: conv2d columns, 2: conv2d weight-gradient partials,
+// 3: conv2d padded weights).  Slot 0 is the split-K scratch above; the products conv2d runs
+// may use that one at the same time, hence separate slots.
+int workspace_slot(int device, int slot, size_t bytes, void **out) {
+    if (slot == 0) return workspace_get(device, bytes, out);
+    DeviceState *d;
+    int rc = device_state(device, &d);
+    if (rc != TTB_OK) return rc;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (slot < 1 || slot > kExtraSlots) {
+        set_error("workspace slot %d out of range", slot);
+        return TTB_EINVAL;
+    }
+    void *&buf = d->extra[slot - 1];
+    size_t &have = d->extra_bytes[slot - 1];
+    if (have < bytes) {
+        if (buf) cudaFree(buf);
+        buf = nullptr;
+        have = 0;
+        cudaError_t e = cudaMalloc(&buf, bytes);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(workspace slot)");
+        have = bytes;
+    }
+    *out = buf;
     return TTB_OK;
 }
 
@@ -358,6 +391,9 @@ int resolve_problem(const ttb_view *lhs, const ttb_view *rhs, void *out, int dty
     return resolve(lhs, rhs, out, 0, nullptr, dtype, device, stream, p);
 }
 
+static int dispatch(const Problem &p);
+int dispatch_problem(const Problem &p) { return dispatch(p); }
+
 static int dispatch(const Problem &p) {
     DeviceState *d;
     int rc = device_state(p.device, &d);
@@ -437,6 +473,39 @@ TTB_API int ttb_batched_matmul_strided_out(const ttb_view *lhs, const ttb_view *
     Problem p{};
     int rc = resolve(lhs, rhs, out, out_offset, out_stride, dtype, device_id, stream, &p);
     if (rc != TTB_OK) return rc;
+    return dispatch(p);
+}
+
+TTB_API int ttb_batched_matmul_fused(const ttb_view *lhs, const ttb_view *rhs, void *out, int64_t out_offset,
+                                     const int64_t out_stride[3], const ttb_view *addend, int activation,
+                                     int dtype, int device_id, void *stream) {
+    Problem p{};
+    int rc = resolve(lhs, rhs, out, out_offset, out_stride, dtype, device_id, stream, &p);
+    if (rc != TTB_OK) return rc;
+    if (activation != TTB_ACT_NONE && activation != TTB_ACT_RELU) {
+        set_error("unknown activation %d", activation);
+        return TTB_EINVAL;
+    }
+    if (activation == TTB_ACT_RELU && dtype != TTB_F32 && dtype != TTB_F64) {
+        set_error("relu in the epilogue needs a floating-point dtype");
+        return TTB_EDTYPE;
+    }
+    if (addend) {
+        rc = check_view(addend, "addend");
+        if (rc != TTB_OK) return rc;
+        if (addend->size[0] != p.B || addend->size[1] != p.N || addend->size[2] != p.M) {
+            set_error("addend is [%lld,%lld,%lld], the product is [%lld,%lld,%lld]",
+                      static_cast<long long>(addend->size[0]), static_cast<long long>(addend->size[1]),
+                      static_cast<long long>(addend->size[2]), static_cast<long long>(p.B),
+                      static_cast<long long>(p.N), static_cast<long long>(p.M));
+            return TTB_ESHAPE;
+        }
+        p.d = static_cast<const char *>(addend->data) + addend->offset * dtype_size(dtype);
+        p.d_sb = addend->stride[0];
+        p.d_si = addend->stride[1];
+        p.d_sj = addend->stride[2];
+    }
+    p.act = activation;
     return dispatch(p);
 }
 
@@ -719,6 +788,14 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         g_opt.tc_debug = static_cast<int>(value);
         return TTB_OK;
     }
+    if (!strcmp(key, "conv_columns_mb")) {
+        if (value < 1 || value > 65536) {
+            set_error("conv_columns_mb must be 1..65536");
+            return TTB_EINVAL;
+        }
+        g_opt.conv_columns_mb = static_cast<int>(value);
+        return TTB_OK;
+    }
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
@@ -733,6 +810,7 @@ TTB_API int64_t ttb_get_option(const char *key) {
     if (!strcmp(key, "mask_big")) return g_opt.mask_big;
     if (!strcmp(key, "tc_profile")) return g_opt.tc_profile;
     if (!strcmp(key, "streamk")) return g_opt.streamk;
+    if (!strcmp(key, "conv_columns_mb")) return g_opt.conv_columns_mb;
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
