@@ -392,12 +392,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: how C is all-gathered (fused into the GEMM kernel, or NCCL after it)")
-    ap.add_argument("--workload", default="c4", choices=["c1", "c2", "c3", "c4", "c4b", "c5"],
-                    help="c4 (default) is the headline configuration; the others are the remaining "
-                         "BASELINE configurations, timed the same way (bench_configs.py)")
+    ap.add_argument("--workload", default="c4", choices=["c1", "c2", "c3", "c4", "c4b", "c5", "conv", "linear"],
+                    help="c4 (default) is the headline configuration; c1..c5 are the remaining "
+                         "BASELINE configurations, timed the same way (bench_configs.py); conv and linear "
+                         "are the callers either side of the path (bench_callers.py)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in ("conv", "linear"):
+        import bench_callers
+
+        bench_callers.run(args, measured_peaks, ClockSampler, load_reference)
     elif args.workload != "c4":
         import bench_configs
 

@@ -48,58 +48,87 @@ struct SumOf<T, false> {
     using type = std::make_unsigned_t<T>;
 };
 
-// columns[bz][row][hw] = x[b0 + bz][c][S*h + p - P][S*w + q - P] or 0 outside the image.
-// grid: (hw blocks, row blocks, batch items of this chunk).  Pure data movement, so it is
-// instantiated per element size only.
+// Four elements moved as one (16 bytes for 4-byte types; 8-byte types take two 16-byte stores).
+template <typename U>
+struct alignas(sizeof(U) * 4 <= 16 ? sizeof(U) * 4 : 16) Vec4 {
+    U v[4];
+};
+
+// columns[bz][c*K*K + p*K + q][hw] = x[b0 + bz][c][S*h + p - P][S*w + q - P] or 0 outside the
+// image.  grid: (blocks of 256 x 4 output pixels, C_in, batch items of this group).  A thread owns
+// four consecutive output pixels: it derives their (h, w) once, then walks the K*K rows of its
+// channel, writing one aligned vector per row (the row pitch is a multiple of 32 elements, so
+// the vector never crosses a row; pixels past H_out*W_out land in the pitch padding as zeros).
+// Pure data movement, so it is instantiated per element size only.
 template <typename U>
 __global__ void __launch_bounds__(256) im2col_kernel(const U *__restrict__ x, U *__restrict__ cols, ConvGeom g,
                                                      long long b0) {
-    const long long hw = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
-    if (hw >= g.hw) return;
-    const int h = static_cast<int>(hw / g.W_out), w = static_cast<int>(hw % g.W_out);
+    const long long hw0 = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) * 4;
+    if (hw0 >= g.hw) return;
+    int hs[4], ws[4];
+    bool live[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const long long hw = hw0 + j;
+        live[j] = hw < g.hw;
+        hs[j] = static_cast<int>(hw / g.W_out) * g.S - g.P;
+        ws[j] = static_cast<int>(hw % g.W_out) * g.S - g.P;
+    }
+    const int c = blockIdx.y;
     const long long bz = blockIdx.z;
-    const U *xb = x + (b0 + bz) * g.C_in * g.H_in * g.W_in;
-    U *cb = cols + bz * g.rows * g.pitch;
-    const int KK = g.K * g.K;
-    for (long long row = blockIdx.y; row < g.rows; row += gridDim.y) {
-        const int c = static_cast<int>(row / KK), pq = static_cast<int>(row % KK);
-        const int p = pq / g.K, q = pq % g.K;
-        const int h_in = g.S * h + p - g.P, w_in = g.S * w + q - g.P;
-        U v = 0;
-        if (h_in >= 0 && w_in >= 0 && h_in < g.H_in && w_in < g.W_in)
-            v = xb[(static_cast<long long>(c) * g.H_in + h_in) * g.W_in + w_in];
-        cb[row * g.pitch + hw] = v;
+    const U *xc = x + ((b0 + bz) * g.C_in + c) * static_cast<long long>(g.H_in) * g.W_in;
+    U *cr = cols + (bz * g.rows + static_cast<long long>(c) * g.K * g.K) * g.pitch + hw0;
+    for (int p = 0; p < g.K; ++p) {
+        for (int q = 0; q < g.K; ++q) {
+            Vec4<U> out;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int h_in = hs[j] + p, w_in = ws[j] + q;
+                const bool inside = live[j] && h_in >= 0 && w_in >= 0 && h_in < g.H_in && w_in < g.W_in;
+                out.v[j] = inside ? xc[static_cast<long long>(h_in) * g.W_in + w_in] : U(0);
+            }
+            *reinterpret_cast<Vec4<U> *>(cr) = out;
+            cr += g.pitch;
+        }
     }
 }
 
 // grad_x[b][c][hi][wi] = sum over (p, q), ascending, of columns[b][c*KK + p*K + q][h*W_out + w]
-// with S*h + p - P == hi and S*w + q - P == wi.
-template <typename T>
+// with S*h + p - P == hi and S*w + q - P == wi.  UNIT: stride 1 (no division per tap).
+template <typename T, bool UNIT>
 __global__ void __launch_bounds__(256) col2im_kernel(const T *__restrict__ cols, T *__restrict__ gx, ConvGeom g,
-                                                     long long b0, long long total) {
+                                                     long long b0) {
     using A = typename SumOf<T>::type;
-    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
-    if (idx >= total) return;
-    const int wi = static_cast<int>(idx % g.W_in);
-    const int hi = static_cast<int>((idx / g.W_in) % g.H_in);
-    const int c = static_cast<int>((idx / (static_cast<long long>(g.W_in) * g.H_in)) % g.C_in);
-    const long long bz = idx / (static_cast<long long>(g.W_in) * g.H_in * g.C_in);
-    const T *cb = cols + bz * g.rows * g.pitch + static_cast<long long>(c) * g.K * g.K * g.pitch;
+    const int pix = blockIdx.x * 256 + threadIdx.x;  // grid: (pixel blocks, C_in, batch items of this group)
+    if (pix >= g.H_in * g.W_in) return;
+    const int hi = pix / g.W_in, wi = pix % g.W_in;
+    const int c = blockIdx.y;
+    const long long bz = blockIdx.z;
+    const T *cb = cols + (bz * g.rows + static_cast<long long>(c) * g.K * g.K) * g.pitch;
     A s = A(0);
     for (int p = 0; p < g.K; ++p) {
         const int hh = hi + g.P - p;
-        if (hh < 0 || hh % g.S != 0) continue;
-        const int h = hh / g.S;
+        if (hh < 0) break;  // larger p only lowers hh
+        int h = hh;
+        if (!UNIT) {
+            if (hh % g.S != 0) continue;
+            h = hh / g.S;
+        }
         if (h >= g.H_out) continue;
+        const T *row = cb + static_cast<long long>(p) * g.K * g.pitch + static_cast<long long>(h) * g.W_out;
         for (int q = 0; q < g.K; ++q) {
             const int ww = wi + g.P - q;
-            if (ww < 0 || ww % g.S != 0) continue;
-            const int w = ww / g.S;
+            if (ww < 0) break;
+            int w = ww;
+            if (!UNIT) {
+                if (ww % g.S != 0) continue;
+                w = ww / g.S;
+            }
             if (w >= g.W_out) continue;
-            s = s + static_cast<A>(cb[static_cast<long long>(p * g.K + q) * g.pitch + h * g.W_out + w]);
+            s = s + static_cast<A>(row[static_cast<long long>(q) * g.pitch + w]);
         }
     }
-    gx[(b0 + bz) * g.C_in * g.H_in * g.W_in + (idx - bz * g.C_in * g.H_in * g.W_in)] = static_cast<T>(s);
+    gx[(((b0 + bz) * g.C_in + c) * g.H_in + hi) * static_cast<long long>(g.W_in) + wi] = static_cast<T>(s);
 }
 
 // out[i] = (accumulate ? out[i] : 0) + part[0][i] + part[1][i] + ... in that order.
@@ -114,26 +143,25 @@ __global__ void __launch_bounds__(256) sum_parts_kernel(const T *__restrict__ pa
     out[i] = static_cast<T>(s);
 }
 
-// grad_bias[m] = sum over b, h, w of g_out[b][m][h][w].  One CTA per channel.  Integers wrap;
-// floats are summed in double and rounded once.
+// part[b][m] = sum over h, w of g_out[b][m][h][w]: one CTA per (channel, batch item); the batch
+// items are then added in ascending order by sum_parts_kernel.  Integers wrap; a float row is
+// summed in double and rounded once.
 template <typename T>
-__global__ void __launch_bounds__(256) channel_sum_kernel(const T *__restrict__ go, T *__restrict__ gb, long long B,
+__global__ void __launch_bounds__(256) channel_sum_kernel(const T *__restrict__ go, T *__restrict__ part,
                                                           long long C_out, long long hw) {
     using A = std::conditional_t<std::is_floating_point_v<T>, double, typename SumOf<T>::type>;
     __shared__ A red[256];
-    const long long m = blockIdx.x;
+    const long long m = blockIdx.x, b = blockIdx.y;
+    const T *src = go + (b * C_out + m) * hw;
     A s = A(0);
-    for (long long b = 0; b < B; ++b) {
-        const T *src = go + (b * C_out + m) * hw;
-        for (long long i = threadIdx.x; i < hw; i += 256) s = s + static_cast<A>(src[i]);
-    }
+    for (long long i = threadIdx.x; i < hw; i += 256) s = s + static_cast<A>(src[i]);
     red[threadIdx.x] = s;
     __syncthreads();
     for (int step = 128; step > 0; step >>= 1) {
         if (threadIdx.x < step) red[threadIdx.x] = red[threadIdx.x] + red[threadIdx.x + step];
         __syncthreads();
     }
-    if (threadIdx.x == 0) gb[m] = static_cast<T>(red[0]);
+    if (threadIdx.x == 0) part[b * C_out + m] = static_cast<T>(red[0]);
 }
 
 // dst[r][0..cols) = src[r][0..cols), row pitch `pitch` (>= cols); the padding is zeroed.
@@ -148,8 +176,7 @@ __global__ void __launch_bounds__(256) pad_rows_kernel(const U *__restrict__ src
 
 template <typename U>
 int launch_im2col(const void *x, void *cols, const ConvGeom &g, long long b0, long long nb, cudaStream_t st) {
-    const unsigned gy = static_cast<unsigned>(g.rows < 65535 ? g.rows : 65535);
-    dim3 grid(static_cast<unsigned>((g.hw + 255) / 256), gy, static_cast<unsigned>(nb));
+    dim3 grid(static_cast<unsigned>((g.hw + 1023) / 1024), static_cast<unsigned>(g.C_in), static_cast<unsigned>(nb));
     im2col_kernel<U><<<grid, 256, 0, st>>>(static_cast<const U *>(x), static_cast<U *>(cols), g, b0);
     cudaError_t e = cudaGetLastError();
     note_launch(-1, 1);
@@ -167,9 +194,12 @@ int im2col(const void *x, void *cols, const ConvGeom &g, long long b0, long long
 
 template <typename T>
 int typed_col2im(const void *cols, void *gx, const ConvGeom &g, long long b0, long long nb, cudaStream_t st) {
-    const long long total = nb * g.C_in * g.H_in * g.W_in;
-    col2im_kernel<T><<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(static_cast<const T *>(cols),
-                                                                                 static_cast<T *>(gx), g, b0, total);
+    dim3 grid(static_cast<unsigned>((static_cast<long long>(g.H_in) * g.W_in + 255) / 256),
+              static_cast<unsigned>(g.C_in), static_cast<unsigned>(nb));
+    if (g.S == 1)
+        col2im_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T *>(cols), static_cast<T *>(gx), g, b0);
+    else
+        col2im_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T *>(cols), static_cast<T *>(gx), g, b0);
     cudaError_t e = cudaGetLastError();
     note_launch(-1, 1);
     return e == cudaSuccess ? TTB_OK : cuda_fail(e, "col2im_kernel launch");
@@ -186,9 +216,9 @@ int typed_sum_parts(const void *part, void *out, long long n, int parts, int acc
 }
 
 template <typename T>
-int typed_channel_sum(const void *go, void *gb, long long B, long long C_out, long long hw, cudaStream_t st) {
-    channel_sum_kernel<T><<<static_cast<unsigned>(C_out), 256, 0, st>>>(static_cast<const T *>(go),
-                                                                        static_cast<T *>(gb), B, C_out, hw);
+int typed_channel_sum(const void *go, void *part, long long B, long long C_out, long long hw, cudaStream_t st) {
+    dim3 grid(static_cast<unsigned>(C_out), static_cast<unsigned>(B));
+    channel_sum_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T *>(go), static_cast<T *>(part), C_out, hw);
     cudaError_t e = cudaGetLastError();
     note_launch(-1, 1);
     return e == cudaSuccess ? TTB_OK : cuda_fail(e, "channel_sum_kernel launch");
@@ -233,6 +263,10 @@ int make_geom(const ttb_conv2d_desc *d, int dtype, ConvGeom *g, size_t *es) {
         set_error("conv2d: tensor sizes beyond 2^31 - 1 elements");
         return TTB_ELIMIT;
     }
+    if (d->c_in > 65535 || d->c_out > 65535) {
+        set_error("conv2d: more than 65535 channels");
+        return TTB_ELIMIT;
+    }
     g->C_in = static_cast<int>(d->c_in);
     g->H_in = static_cast<int>(d->h_in);
     g->W_in = static_cast<int>(d->w_in);
@@ -254,6 +288,7 @@ long long chunk_batches(const ConvGeom &g, long long B, size_t es) {
     const size_t per = static_cast<size_t>(g.rows) * g.pitch * es;
     long long nb = static_cast<long long>(conv_columns_budget() / (per ? per : 1));
     if (nb < 1) nb = 1;
+    if (nb > 65535) nb = 65535;  // batch items of a group are grid.z of the unroll kernels
     return nb < B ? nb : B;
 }
 
@@ -374,7 +409,9 @@ extern "C" TTB_API int ttb_conv2d_backward(const void *grad_out, const void *inp
     rc = workspace_slot(device_id, 1, static_cast<size_t>(nb_max) * g.rows * g.pitch * es, &cols);
     if (rc != TTB_OK) return rc;
     const long long wn = static_cast<long long>(g.C_out) * g.rows;
-    rc = workspace_slot(device_id, 2, static_cast<size_t>(nb_max) * wn * es, &parts);
+    // also holds the per-item channel sums of grad_bias afterwards
+    const long long parts_elems = nb_max * wn > B * g.C_out ? nb_max * wn : B * g.C_out;
+    rc = workspace_slot(device_id, 2, static_cast<size_t>(parts_elems) * es, &parts);
     if (rc != TTB_OK) return rc;
     const void *w = nullptr;
     long long w_pitch = 0;
@@ -437,7 +474,10 @@ extern "C" TTB_API int ttb_conv2d_backward(const void *grad_out, const void *inp
         if (rc != TTB_OK) return rc;
     }
     if (grad_bias) {
-        rc = TTB_BY_DTYPE(dtype, typed_channel_sum, grad_out, grad_bias, B, static_cast<long long>(g.C_out), g.hw, st);
+        rc = TTB_BY_DTYPE(dtype, typed_channel_sum, grad_out, parts, B, static_cast<long long>(g.C_out), g.hw, st);
+        if (rc != TTB_OK) return rc;
+        rc = TTB_BY_DTYPE(dtype, typed_sum_parts, parts, grad_bias, static_cast<long long>(g.C_out), static_cast<int>(B),
+                          0, st);
         if (rc != TTB_OK) return rc;
     }
     return TTB_OK;
