@@ -36,6 +36,7 @@ class Variant(enum.IntEnum):
     DMMA_F64 = 3
     SIMT_SPLITK = 4
     TCGEN05_2CTA = 5
+    TCGEN05_I8LIMB = 6
 
 
 class _View(ctypes.Structure):

@@ -35,6 +35,7 @@ SOURCES = [
     "gemm_simt.cu",
     "gemm_f32_tcgen05.cu",
     "gemm_f64_dmma.cu",
+    "gemm_i32_tcgen05.cu",
     "conv2d.cu",
 ]
 

@@ -336,5 +336,27 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
     }
 }
 
+// Instruction descriptor for kind::i8: unsigned 8-bit inputs (A/B format 0), s32 accumulate
+// (D format 2), no saturation (bit 3 = 0: sums wrap mod 2^32), both operands K-major.
+// K of one MMA is 32.
+__host__ __device__ constexpr uint32_t make_idesc_u8(int m, int n) {
+    return (2u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+constexpr uint64_t kSwizzleNone = 0;
+
+// D[tmem] (+)= A * B with 8-bit integer inputs (kind::i8), one CTA.
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "setp.ne.b32 P, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, P;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 }  // namespace ptx
 }  // namespace ttb

@@ -35,6 +35,7 @@ struct Options {
     int tc_profile = 0;
     int tc_debug = 0;
     int conv_columns_mb = 2048;  // budget of conv2d's unrolled-columns workspace
+    int int_tensor = 1;          // i32 products may use the int8 tensor-core kernel
 };
 Options g_opt;
 
@@ -424,6 +425,12 @@ static int dispatch(const Problem &p) {
                 return TTB_EUNSUPPORTED;
             }
             return launch_f64_dmma(p);
+        case TTB_VARIANT_TCGEN05_I8LIMB:
+            if (!i32_tcgen05_eligible(p, why, sizeof(why))) {
+                set_error("forced int8-plane tcgen05 variant cannot take this call: %s", why);
+                return TTB_EUNSUPPORTED;
+            }
+            return launch_i32_tcgen05(p);
         default: break;
     }
     // Automatic dispatch.
@@ -445,6 +452,13 @@ static int dispatch(const Problem &p) {
     if (p.dtype == TTB_F64) {
         if (p.N > 16 && p.M > 16 && f64_dmma_eligible(p)) return launch_f64_dmma(p);
         return launch_simt(p, g_opt.splitk != 0);
+    }
+    if (p.dtype == TTB_I32 && g_opt.int_tensor != 0) {
+        // Ten int8 tensor-core products of byte planes beat the 32-bit multiply-add pipe once
+        // the 128 x 128 tiles are reasonably full and there is some K to amortise the epilogue.
+        const bool big = p.N >= 64 && p.M >= 64 && p.K >= 64 &&
+                         static_cast<double>(p.N) * p.M * p.K * p.B >= 256.0 * 256.0 * 256.0;
+        if (big && i32_tcgen05_eligible(p, why, sizeof(why))) return launch_i32_tcgen05(p);
     }
     return launch_simt(p, g_opt.splitk != 0);
 }
@@ -723,6 +737,7 @@ TTB_API const char *ttb_variant_name(int variant) {
         case TTB_VARIANT_DMMA_F64: return "dmma_f64";
         case TTB_VARIANT_SIMT_SPLITK: return "simt_splitk";
         case TTB_VARIANT_TCGEN05_2CTA: return "tcgen05_3xtf32_2cta";
+        case TTB_VARIANT_TCGEN05_I8LIMB: return "tcgen05_i8_byte_planes";
         default: return "unknown";
     }
 }
@@ -733,7 +748,7 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         return TTB_EINVAL;
     }
     if (!strcmp(key, "force_variant")) {
-        if (value < 0 || value > TTB_VARIANT_TCGEN05_2CTA) {
+        if (value < 0 || value > TTB_VARIANT_TCGEN05_I8LIMB) {
             set_error("force_variant: %lld is not a variant", static_cast<long long>(value));
             return TTB_EINVAL;
         }
@@ -788,6 +803,10 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         g_opt.tc_debug = static_cast<int>(value);
         return TTB_OK;
     }
+    if (!strcmp(key, "int_tensor")) {
+        g_opt.int_tensor = value != 0;
+        return TTB_OK;
+    }
     if (!strcmp(key, "conv_columns_mb")) {
         if (value < 1 || value > 65536) {
             set_error("conv_columns_mb must be 1..65536");
@@ -811,6 +830,7 @@ TTB_API int64_t ttb_get_option(const char *key) {
     if (!strcmp(key, "tc_profile")) return g_opt.tc_profile;
     if (!strcmp(key, "streamk")) return g_opt.streamk;
     if (!strcmp(key, "conv_columns_mb")) return g_opt.conv_columns_mb;
+    if (!strcmp(key, "int_tensor")) return g_opt.int_tensor;
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
