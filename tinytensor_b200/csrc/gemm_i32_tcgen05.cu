@@ -19,9 +19,10 @@
 //                views need no copy;
 //   warp 1       MMA issuer: per K block ten tcgen05.mma into four TMEM accumulators
 //                (4 x 128 columns = all of tensor memory);
-//   warps 4-7    epilogue: tcgen05.ld the four accumulators 16 columns at a time, shift, add,
-//                add the fused addend if any, store C;
-//   warps 8-11   converters: split the raw tiles into four byte planes per operand, each a
+//   warps 4-11   epilogue (two warps per TMEM lane quarter, 64 columns each): tcgen05.ld the
+//                four accumulators 16 columns at a time, shift, add, add the fused addend if
+//                any, store C;
+//   warps 12-15  converters: split the raw tiles into four byte planes per operand, each a
 //                K-major 128 x 32-byte tile in the unswizzled core-matrix layout
 //                ([K half][row][16 bytes]), fence.proxy.async, signal.
 // The MMAs never read the raw tiles, so a raw slot is released by the converters and a plane
@@ -51,8 +52,9 @@ constexpr int PLANE_BYTES = BM * BK;         // 4 KiB: one byte plane of one ope
 constexpr int PLANE_RING_OFFSET = RAW_STAGES * STAGE_BYTES;
 constexpr int SMEM_BYTES = (RAW_STAGES + PLANE_STAGES) * STAGE_BYTES + 1024;
 constexpr int MN_BOX_BYTES = 32 * BK * 4;    // one MN-major TMA box: 32 (MN) x BK (K)
-constexpr int NUM_THREADS = 384;
-constexpr int FIRST_EPI_WARP = 4, FIRST_CONV_WARP = 8, NUM_CONV_WARPS = 4;
+constexpr int EPI_WARPS = 8;           // two per TMEM lane quarter: each takes 64 of a tile's 128 columns
+constexpr int FIRST_EPI_WARP = 4, FIRST_CONV_WARP = FIRST_EPI_WARP + EPI_WARPS, NUM_CONV_WARPS = 4;
+constexpr int NUM_THREADS = (FIRST_CONV_WARP + NUM_CONV_WARPS) * 32;
 constexpr int TMEM_COLS = 512;        // P_0 .. P_3, 128 columns each
 
 struct alignas(64) I8Args {
@@ -157,7 +159,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
             mbar_init(&plane_empty_bar[s], 1);
         }
         mbar_init(&acc_full_bar, 1);
-        mbar_init(&acc_empty_bar, 4);
+        mbar_init(&acc_empty_bar, EPI_WARPS);
         mbar_init(&drain_bar, 1);
         abort_flag_s = 0;
         fence_mbar_init();
@@ -287,6 +289,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
     } else if (warp >= FIRST_EPI_WARP && warp < FIRST_CONV_WARP) {
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;  // TMEM lanes [32 * quarter, +32)
+        const int col_half = (warp - FIRST_EPI_WARP) >> 2;  // columns [64 * col_half, +64) of the tile
         uint32_t acc_phase = 0;
         bool ok = true;
         const bool vec_ok = args.c_sj == 1 && (args.c_si & 3) == 0 && (args.c_sb & 3) == 0 &&
@@ -307,39 +310,45 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
             const int32_t *drow = args.d ? args.d + static_cast<long long>(b) * args.d_sb +
                                                static_cast<long long>(row) * args.d_si
                                          : nullptr;
-#pragma unroll 1
-            for (int q = 0; q < BM / 16; ++q) {
-                uint32_t p0[16], p1[16], p2[16], p3[16];
-                tmem_ld_32x16(t_row + static_cast<uint32_t>(0 * BM + q * 16), p0);
-                tmem_ld_32x16(t_row + static_cast<uint32_t>(1 * BM + q * 16), p1);
-                tmem_ld_32x16(t_row + static_cast<uint32_t>(2 * BM + q * 16), p2);
-                tmem_ld_32x16(t_row + static_cast<uint32_t>(3 * BM + q * 16), p3);
+            // Read this warp's 32 rows x 64 columns of all four accumulators, combining as they
+            // arrive, then hand tensor memory back to the MMA thread BEFORE storing: the stores of
+            // this tile overlap the next tile's products.
+            uint32_t out[64];
+            const uint32_t t_col = t_row + static_cast<uint32_t>(col_half * 64);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                uint32_t p0[8], p1[8], p2[8], p3[8];
+                tmem_ld_32x8(t_col + static_cast<uint32_t>(0 * BM + q * 8), p0);
+                tmem_ld_32x8(t_col + static_cast<uint32_t>(1 * BM + q * 8), p1);
+                tmem_ld_32x8(t_col + static_cast<uint32_t>(2 * BM + q * 8), p2);
+                tmem_ld_32x8(t_col + static_cast<uint32_t>(3 * BM + q * 8), p3);
                 tmem_ld_wait();
-                const int col0 = tn * BM + q * 16;
-                if (row < args.N && col0 < args.M) {
-                    uint32_t out[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        out[j] = p0[j] + (p1[j] << 8) + (p2[j] << 16) + (p3[j] << 24);
-                        if (drow && col0 + j < args.M)
-                            out[j] += static_cast<uint32_t>(drow[static_cast<long long>(col0 + j) * args.d_sj]);
-                    }
-                    if (vec_ok && col0 + 16 <= args.M) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(crow + col0);
-#pragma unroll
-                        for (int v = 0; v < 4; ++v)
-                            dst[v] = make_uint4(out[4 * v], out[4 * v + 1], out[4 * v + 2], out[4 * v + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (col0 + j < args.M)
-                                crow[static_cast<long long>(col0 + j) * args.c_sj] = static_cast<int32_t>(out[j]);
-                    }
-                }
+                for (int j = 0; j < 8; ++j) out[q * 8 + j] = p0[j] + (p1[j] << 8) + (p2[j] << 16) + (p3[j] << 24);
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty_bar);
+            const int col0 = tn * BM + col_half * 64;
+            if (row < args.N && col0 < args.M) {
+                if (drow) {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j)
+                        if (col0 + j < args.M)
+                            out[j] += static_cast<uint32_t>(drow[static_cast<long long>(col0 + j) * args.d_sj]);
+                }
+                if (vec_ok && col0 + 64 <= args.M) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(crow + col0);
+#pragma unroll
+                    for (int v = 0; v < 16; ++v)
+                        dst[v] = make_uint4(out[4 * v], out[4 * v + 1], out[4 * v + 2], out[4 * v + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j)
+                        if (col0 + j < args.M)
+                            crow[static_cast<long long>(col0 + j) * args.c_sj] = static_cast<int32_t>(out[j]);
+                }
+            }
             acc_phase ^= 1u;
         }
     } else if (warp >= FIRST_CONV_WARP) {
