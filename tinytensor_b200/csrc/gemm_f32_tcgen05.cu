@@ -60,13 +60,16 @@ constexpr int BM = 128;              // lhs rows per CTA
 constexpr int BNC = 128;             // rhs columns loaded per CTA
 constexpr int BK = 32;               // fp32 per K block = 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;            // K of one tcgen05.mma kind::tf32
-constexpr int STAGES = 5;             // raw ring: tiles as TMA delivers them (deep: hides load latency)
+constexpr int STAGES = 4;             // raw ring: tiles as TMA delivers them (deep: hides load latency)
 constexpr int SMALL_STAGES = 2;       // small ring: written by the converters just ahead of the MMAs
 constexpr int TILE_BYTES = BM * BK * 4;        // 16 KiB: one operand tile
 constexpr int RAW_BYTES = 2 * TILE_BYTES;      // raw A + raw B
 constexpr int STAGE_BYTES = RAW_BYTES;         // one slot of either ring
 constexpr int SMALL_RING_OFFSET = STAGES * STAGE_BYTES;
-constexpr int SMEM_BYTES = (STAGES + SMALL_STAGES) * STAGE_BYTES + 1024;  // + alignment slack
+constexpr int OUT_STAGING_OFFSET = (STAGES + SMALL_STAGES) * STAGE_BYTES;  // epilogue store staging
+constexpr int OUT_STAGING_WARP_BYTES = 32 * 128;  // 32 rows x 32 fp32 per epilogue warp
+constexpr int OUT_STAGING_BYTES = 8 * OUT_STAGING_WARP_BYTES;              // up to 8 epilogue warps
+constexpr int SMEM_BYTES = OUT_STAGING_OFFSET + OUT_STAGING_BYTES + 1024;  // + alignment slack
 constexpr int MN_BOX_BYTES = 32 * BK * 4;      // one MN-major TMA box: 32 (MN) x BK (K)
 constexpr int H_TILE_BYTES = BM * BK * 2;      // 8 KiB: one bf16 operand tile of the hybrid split
 constexpr int DEFAULT_K_CHUNK = 8;             // K blocks summed inside TMEM
@@ -749,9 +752,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     break;
                 }
             }
-            if (row < args.N && col0 < args.M) {
+            if (col0 < args.M) {
+                const bool mine = row < args.N;
                 float *crow = args.c + static_cast<long long>(b) * args.c_sb + static_cast<long long>(row) * args.c_si;
-                if (args.d != nullptr) {
+                if (mine && args.d != nullptr) {
                     // Fused addend.  The thread that adds d[b,row,col] is the one that stores
                     // c[b,row,col], so d may be C itself (accumulation).
                     const float *drow =
@@ -780,12 +784,44 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 #pragma unroll
                     for (int j = 0; j < 128; ++j) sum[j] = sum[j] < 0.0f ? 0.0f : sum[j];
                 }
-                if (vec_ok && col0 + 128 <= args.M) {
-                    float4 *dst = reinterpret_cast<float4 *>(crow + col0);
+                if (vec_ok) {
+                    // Row-contiguous C: a thread holds one row, so storing from registers would make
+                    // every store instruction touch 32 different 128-byte lines.  Instead each warp
+                    // passes 32 columns at a time through its 4 KiB of shared memory (16-byte chunks
+                    // XORed with the row, so both directions are conflict-free) and stores with 8
+                    // lanes per row: one instruction writes four complete 128-byte lines.
+                    uint8_t *stg = tiles + OUT_STAGING_OFFSET + epi_warp * OUT_STAGING_WARP_BYTES;
+                    const int row_base = row - lane;
+                    float *cbase = args.c + static_cast<long long>(b) * args.c_sb;
 #pragma unroll
-                    for (int q = 0; q < 32; ++q)
-                        dst[q] = make_float4(sum[4 * q], sum[4 * q + 1], sum[4 * q + 2], sum[4 * q + 3]);
-                } else {
+                    for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<float4 *>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                                make_float4(sum[ch * 32 + 4 * c], sum[ch * 32 + 4 * c + 1], sum[ch * 32 + 4 * c + 2],
+                                            sum[ch * 32 + 4 * c + 3]);
+                        __syncwarp();
+                        const int cc = lane & 7;
+                        const int gcol = col0 + ch * 32 + 4 * cc;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = 4 * i + (lane >> 3);
+                            const float4 v = *reinterpret_cast<const float4 *>(stg + r * 128 + ((cc ^ (r & 7)) << 4));
+                            const int grow = row_base + r;
+                            if (grow < args.N && !(args.dbg & 32)) {
+                                float *dst = cbase + static_cast<long long>(grow) * args.c_si + gcol;
+                                if (gcol + 4 <= args.M) {
+                                    *reinterpret_cast<float4 *>(dst) = v;
+                                } else {
+                                    if (gcol < args.M) dst[0] = v.x;
+                                    if (gcol + 1 < args.M) dst[1] = v.y;
+                                    if (gcol + 2 < args.M) dst[2] = v.z;
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
+                } else if (mine) {
 #pragma unroll
                     for (int j = 0; j < 128; ++j)
                         if (col0 + j < args.M) crow[static_cast<long long>(col0 + j) * args.c_sj] = sum[j];
