@@ -67,9 +67,8 @@ int sm_count(int device, int *out);
 // Device buffer for the tcgen05 kernel's wait-cycle counters, or nullptr when the
 // "tc_profile" option is off.
 long long *profile_ptr(int device);
-// Stream-K workspace (partial-sum slots, ready flags) of (device, stream) and this launch's number.
-int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags,
-                      unsigned int *epoch);
+// Stream-K workspace (partial-sum slots, ready flags) of (device, stream).
+int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags);
 
 // Per-dtype launchers.  Each returns a ttb_status.
 int launch_simt(const Problem &p, bool allow_splitk);

@@ -99,6 +99,9 @@ struct Cfg {
 struct alignas(64) TcArgs {
     CUtensorMap tmap_a;
     CUtensorMap tmap_b;
+    CUtensorMap tmap_c;  // C as {M, N, B} with 32 x 32 boxes, for the epilogue's bulk tensor stores
+    int c_tma;           // tmap_c is valid (C rows contiguous and 16-byte aligned)
+    int c_batch_mul;     // 0 pins the batch coordinate (B == 1)
     float *c;
     long long c_sb, c_si, c_sj;
     const float *d;  // fused epilogue: addend view (bias row / column, or C itself), nullptr = none
@@ -113,8 +116,7 @@ struct alignas(64) TcArgs {
     int mask_big;  // converters also overwrite the raw tile with its masked big part
     int streamk;   // 1: K blocks are dealt out evenly over the units (see Work), else whole tiles
     float *sk_partials;       // stream-K workspace: per unit, CTA and epilogue warp 32 x 128 partial sums
-    unsigned int *sk_flags;   // stream-K flags, one per unit, CTA and epilogue warp: launch number when ready
-    unsigned int sk_epoch;    // this launch's number
+    unsigned int *sk_flags;   // stream-K flags, one per unit, CTA and epilogue warp: 1 while partial sums wait
     int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
     float *peer_c[kMaxPeers];  // their C, laid out exactly like `c` (same offset and strides)
     DeviceStatus *status;
@@ -358,7 +360,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     // all-gather treats the last stored tile specially.
     int n_seg, n_store, last_store_tile;
     if (!args.streamk) {
-        n_seg = unit < args.total_tiles ? (args.total_tiles - unit + units - 1) / units : 0;
+        n_seg = (unit < args.total_tiles && !(args.dbg & 64)) ? (args.total_tiles - unit + units - 1) / units : 0;
         n_store = n_seg;
         last_store_tile = unit + (n_seg - 1) * units;
     } else {
@@ -698,12 +700,18 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 // that owns the tile.  Warp w of the owner reads exactly what warp w wrote here
                 // (same TMEM lanes, same columns), so one flag per warp is all the ordering needed.
                 const long long slot = (static_cast<long long>(unit) * CG + cta_rank) * EPI_WARPS + epi_warp;
-                float4 *dst = reinterpret_cast<float4 *>(args.sk_partials + (slot * 32 + lane) * 128);
+                // Slot layout [32 float4 steps][32 lanes]: a warp's store is one contiguous 512 bytes.
+                float4 *dst = reinterpret_cast<float4 *>(args.sk_partials + slot * 4096) + lane;
 #pragma unroll
-                for (int q = 0; q < 32; ++q) dst[q] = make_float4(sum[4 * q], sum[4 * q + 1], sum[4 * q + 2], sum[4 * q + 3]);
+                for (int q = 0; q < 32; ++q)
+                    dst[q * 32] = make_float4(sum[4 * q], sum[4 * q + 1], sum[4 * q + 2], sum[4 * q + 3]);
                 __threadfence();
                 __syncwarp();
-                if (lane == 0) atomicExch(&args.sk_flags[slot], args.sk_epoch);
+                // Flag protocol: the writer raises the flag, the one reader (the tile's owner)
+                // lowers it again after reading, so every flag is back at 0 when the kernel ends.
+                // Nothing depends on a host-side launch counter: a launch recorded into a CUDA
+                // graph replays correctly.
+                if (lane == 0) atomicExch(&args.sk_flags[slot], 1u);
                 continue;
             }
             if (kb1 != num_kb) {
@@ -714,7 +722,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     const long long slot = (static_cast<long long>(q) * CG + cta_rank) * EPI_WARPS + epi_warp;
                     unsigned long long t0 = 0;
                     for (uint32_t spin = 0;; ++spin) {
-                        if (*reinterpret_cast<volatile unsigned int *>(&args.sk_flags[slot]) == args.sk_epoch) break;
+                        if (*reinterpret_cast<volatile unsigned int *>(&args.sk_flags[slot]) != 0u) break;
                         if ((spin & 63u) == 63u) {
                             const unsigned long long now = global_ns();
                             if (t0 == 0) t0 = now;
@@ -729,15 +737,23 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                         break;
                     }
                     __threadfence();
-                    const float4 *src = reinterpret_cast<const float4 *>(args.sk_partials + (slot * 32 + lane) * 128);
+                    const float4 *src = reinterpret_cast<const float4 *>(args.sk_partials + slot * 4096) + lane;
+                    // eight loads in flight at a time: their L2 latencies overlap
 #pragma unroll
-                    for (int v = 0; v < 32; ++v) {
-                        const float4 p = __ldcg(src + v);
-                        sum[4 * v] += p.x;
-                        sum[4 * v + 1] += p.y;
-                        sum[4 * v + 2] += p.z;
-                        sum[4 * v + 3] += p.w;
+                    for (int v0 = 0; v0 < 32; v0 += 8) {
+                        float4 p[8];
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) p[v] = __ldcg(src + (v0 + v) * 32);
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            sum[4 * (v0 + v)] += p[v].x;
+                            sum[4 * (v0 + v) + 1] += p[v].y;
+                            sum[4 * (v0 + v) + 2] += p[v].z;
+                            sum[4 * (v0 + v) + 3] += p[v].w;
+                        }
                     }
+                    __syncwarp();
+                    if (lane == 0) args.sk_flags[slot] = 0u;  // consumed: ready for the next launch
                 }
                 if (!ok) break;
             }
@@ -784,12 +800,37 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 #pragma unroll
                     for (int j = 0; j < 128; ++j) sum[j] = sum[j] < 0.0f ? 0.0f : sum[j];
                 }
-                if (vec_ok) {
-                    // Row-contiguous C: a thread holds one row, so storing from registers would make
-                    // every store instruction touch 32 different 128-byte lines.  Instead each warp
-                    // passes 32 columns at a time through its 4 KiB of shared memory (16-byte chunks
-                    // XORed with the row, so both directions are conflict-free) and stores with 8
-                    // lanes per row: one instruction writes four complete 128-byte lines.
+                if (args.c_tma && args.n_peers == 0) {
+                    // Row-contiguous, 16-byte-aligned C: each warp passes 32 columns at a time
+                    // through its 4 KiB of shared memory, written in the 128-byte-swizzled layout
+                    // (16-byte chunk XOR row) of a 32 x 32 TMA box, and one lane issues a bulk
+                    // tensor store.  The copy engine writes whole lines and clips the box at the
+                    // edges of C; the warp's LSU work is eight 16-byte shared stores per chunk.
+                    uint8_t *stg = tiles + OUT_STAGING_OFFSET + epi_warp * OUT_STAGING_WARP_BYTES;
+                    const int row_base = row - lane;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        // the previous box must have been read out of the staging buffer
+                        if (lane == 0) bulk_wait_read_all();
+                        __syncwarp();
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<float4 *>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                                make_float4(sum[ch * 32 + 4 * c], sum[ch * 32 + 4 * c + 1], sum[ch * 32 + 4 * c + 2],
+                                            sum[ch * 32 + 4 * c + 3]);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        const int gcol = col0 + ch * 32;
+                        if (lane == 0 && row_base < args.N && gcol < args.M && !(args.dbg & 32)) {
+                            tma_store_3d(&args.tmap_c, stg, gcol, row_base, b * args.c_batch_mul);
+                            bulk_commit_group();
+                        }
+                    }
+                } else if (vec_ok) {
+                    // Same staging, stored by the warp itself (fused all-gather: the forwarding
+                    // warps read C back right after the flag below, which plain stores followed by
+                    // a fence order): 8 lanes per row, so one store instruction writes four
+                    // complete 128-byte lines instead of touching 32.
                     uint8_t *stg = tiles + OUT_STAGING_OFFSET + epi_warp * OUT_STAGING_WARP_BYTES;
                     const int row_base = row - lane;
                     float *cbase = args.c + static_cast<long long>(b) * args.c_sb;
@@ -842,6 +883,9 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 }
             }
         }
+        // Bulk tensor stores still in flight read this CTA's shared memory: they must be done
+        // before the CTA gives it up.
+        if (lane == 0) bulk_wait_all();
         if (args.prof && warp == C::FIRST_EPI_WARP && lane == 0) {
             args.prof[blockIdx.x * kProfSlots + kProfEpiAccFull] = w_a;
             args.prof[blockIdx.x * kProfSlots + kProfTotal] = clock64() - kernel_t0;
@@ -1089,16 +1133,25 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     // than units); stream-K deals the K blocks out evenly instead.  It pays when that loss is
     // noticeable and every unit still gets a few K blocks.
     const long long num_kb = (p.K + BK - 1) / BK;
+    const long long total_kb = args.total_tiles * num_kb;
+    // Few tiles (less than half the units would have one): cut every tile's K over several
+    // units, four K blocks or more each, so that most of the GPU works on a small product.
+    const bool sk_small = streamk_opt != 0 && args.total_tiles > 0 && args.total_tiles * 2 <= units && num_kb >= 8;
+    if (sk_small) {
+        long long u = total_kb / 4;
+        if (u > units) u = units;
+        if (u < args.total_tiles) u = args.total_tiles;
+        units = static_cast<int>(u);
+    }
     const long long waves = (args.total_tiles + units - 1) / units;
     const double busy = static_cast<double>(args.total_tiles) / static_cast<double>(waves * units);
     // (a fix-up costs about as much as a few K blocks: only long-K tiles are worth cutting)
-    const bool sk_worth = num_kb >= 64 && args.total_tiles * num_kb / units >= 32;
-    const bool sk_possible = args.total_tiles > 0 && args.total_tiles * num_kb / units >= 4 &&
-                             args.total_tiles * num_kb < 0x7FFFFFFFLL &&
+    const bool sk_worth = (num_kb >= 64 && total_kb / units >= 32) || (sk_small && units > args.total_tiles);
+    const bool sk_possible = args.total_tiles > 0 && total_kb / units >= 4 && total_kb < 0x7FFFFFFFLL &&
                              args.total_tiles / units + 2 <= kMaxSegments;
     bool streamk = streamk_opt > 0 ? sk_possible : (streamk_opt < 0 && sk_possible && sk_worth && busy < 0.93);
     if (streamk) {
-        int rc = streamk_workspace(p.device, p.stream, &args.sk_partials, &args.sk_flags, &args.sk_epoch);
+        int rc = streamk_workspace(p.device, p.stream, &args.sk_partials, &args.sk_flags);
         if (rc != TTB_OK) streamk = false;  // no workspace for this stream: whole tiles
     }
     args.streamk = streamk ? 1 : 0;
@@ -1132,6 +1185,16 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
                             &args.b_batch_mul, why, sizeof(why))) {
         set_error("tensor map: %s", why);
         return TTB_EUNSUPPORTED;
+    }
+    {
+        // C as a "K-major operand": inner dim = columns (unit stride), outer = rows.
+        const OperandView cv{p.c, p.N, p.M, p.B, p.c_si, p.c_sj, p.c_sb};
+        char cw[128] = "";
+        args.c_tma = 0;
+        if (p.c_sb != 0 && classify_operand(cv, 4, cw, sizeof(cw)) == kMajorK &&
+            encode_operand_tmap(&args.tmap_c, cv, kMajorK, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, 32, 32, 32,
+                                &args.c_batch_mul, cw, sizeof(cw)) == 0)
+            args.c_tma = 1;
     }
     args.c = static_cast<float *>(p.c);
     args.c_sb = p.c_sb;

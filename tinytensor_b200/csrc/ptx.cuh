@@ -153,6 +153,24 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, ui
         : "r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// 3-D tiled store this CTA's shared memory -> global (bulk async-group completion).  The box
+// is clipped at the tensor's upper bounds; c0 * elemsize must be a multiple of 16 bytes and no
+// coordinate may be negative.  The shared-memory source must have been written and made
+// visible to the async proxy (fence.proxy.async) before the call.
+__device__ __forceinline__ void tma_store_3d(const void *tmap, const void *smem_src, int32_t c0, int32_t c1,
+                                             int32_t c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 :
+                 : "l"(tmap), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// All of this thread's bulk groups have finished READING their shared-memory source.
+__device__ __forceinline__ void bulk_wait_read_all() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// All of this thread's bulk groups are complete (writes performed).
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

@@ -47,7 +47,6 @@ struct StreamKSet {
     cudaStream_t stream;
     float *partials;
     unsigned int *flags;
-    unsigned int epoch;
 };
 constexpr int kProfCtas = 256;
 constexpr size_t kProfBytes = kProfCtas * 8 * sizeof(long long);
@@ -158,8 +157,7 @@ int sm_count(int device, int *out) {
 // Stream-K workspace of the f32 tensor-core kernel: partial-sum slots and ready flags, one
 // set per (device, stream) so that launches on different streams never share one.  The
 // flags carry the launch number, so nothing has to be cleared between launches.
-int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags,
-                      unsigned int *epoch) {
+int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags) {
     DeviceState *d;
     int rc = device_state(device, &d);
     if (rc != TTB_OK) return rc;
@@ -168,7 +166,6 @@ int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigne
         if (d->sk[i].stream == stream) {
             *partials = d->sk[i].partials;
             *flags = d->sk[i].flags;
-            *epoch = ++d->sk[i].epoch;
             return TTB_OK;
         }
     }
@@ -189,11 +186,9 @@ int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigne
     }
     e = cudaMemset(s.flags, 0, slots * sizeof(unsigned int));
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(stream-K flags)");
-    s.epoch = 1;
     d->sk[d->sk_count++] = s;
     *partials = s.partials;
     *flags = s.flags;
-    *epoch = 1;
     return TTB_OK;
 }
 
@@ -855,6 +850,9 @@ TTB_API int ttb_check_device(int device_id) {
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
     if (h.error != 0) {
         cudaMemset(d->status, 0, sizeof(DeviceStatus));
+        // A kernel that gave up may have left stream-K flags raised: lower them all.
+        for (int i = 0; i < d->sk_count; ++i)
+            cudaMemset(d->sk[i].flags, 0, static_cast<size_t>(d->sms) * 8 * sizeof(unsigned int));
         set_error("device %d: a bounded wait inside a kernel gave up (code %u, detail %u)", device_id, h.error,
                   h.detail);
         return TTB_ETIMEOUT;
