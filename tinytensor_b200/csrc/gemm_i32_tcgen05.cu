@@ -45,12 +45,14 @@ using namespace ptx;
 constexpr int BM = 128;               // rows of A / columns of B per tile
 constexpr int BK = 32;                // int32 per K block = 128 bytes = one swizzle row
 constexpr int RAW_STAGES = 4;         // raw ring (TMA -> converters)
-constexpr int PLANE_STAGES = 3;       // byte-plane ring (converters -> MMAs)
+constexpr int PLANE_STAGES = 2;       // byte-plane ring (converters -> MMAs)
 constexpr int TILE_BYTES = BM * BK * 4;      // 16 KiB: one raw operand tile
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;  // raw A + raw B; a plane slot has the same size
 constexpr int PLANE_BYTES = BM * BK;         // 4 KiB: one byte plane of one operand
 constexpr int PLANE_RING_OFFSET = RAW_STAGES * STAGE_BYTES;
-constexpr int SMEM_BYTES = (RAW_STAGES + PLANE_STAGES) * STAGE_BYTES + 1024;
+constexpr int OUT_STAGING_OFFSET = (RAW_STAGES + PLANE_STAGES) * STAGE_BYTES;  // epilogue store staging
+constexpr int OUT_STAGING_WARP_BYTES = 32 * 128;                               // 32 rows x 32 words per warp
+constexpr int SMEM_BYTES = OUT_STAGING_OFFSET + 8 * OUT_STAGING_WARP_BYTES + 1024;
 constexpr int MN_BOX_BYTES = 32 * BK * 4;    // one MN-major TMA box: 32 (MN) x BK (K)
 constexpr int EPI_WARPS = 8;           // two per TMEM lane quarter: each takes 64 of a tile's 128 columns
 constexpr int FIRST_EPI_WARP = 4, FIRST_CONV_WARP = FIRST_EPI_WARP + EPI_WARPS, NUM_CONV_WARPS = 4;
@@ -60,6 +62,9 @@ constexpr int TMEM_COLS = 512;        // P_0 .. P_3, 128 columns each
 struct alignas(64) I8Args {
     CUtensorMap tmap_a;
     CUtensorMap tmap_b;
+    CUtensorMap tmap_c;  // C as {M, N, B} with 32 x 32 boxes, for the epilogue's bulk tensor stores
+    int c_tma;           // tmap_c is valid (C rows contiguous and 16-byte aligned)
+    int c_batch_mul;     // 0 pins the batch coordinate (B == 1)
     int32_t *c;
     long long c_sb, c_si, c_sj;
     const int32_t *d;  // fused addend view (bias row / column, or C itself), nullptr = none
@@ -330,27 +335,57 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty_bar);
             const int col0 = tn * BM + col_half * 64;
-            if (row < args.N && col0 < args.M) {
-                if (drow) {
+            if (col0 < args.M) {
+                if (drow && row < args.N) {
 #pragma unroll
                     for (int j = 0; j < 64; ++j)
                         if (col0 + j < args.M)
                             out[j] += static_cast<uint32_t>(drow[static_cast<long long>(col0 + j) * args.d_sj]);
                 }
-                if (vec_ok && col0 + 64 <= args.M) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(crow + col0);
+                if (args.c_tma) {
+                    // Row-contiguous, 16-byte-aligned C: 32 columns at a time go through this
+                    // warp's 4 KiB of shared memory in the 128-byte-swizzled layout of a 32 x 32 TMA
+                    // box and leave as one bulk tensor store, which writes whole lines and clips
+                    // at the edges of C.  A thread storing its own row from registers would make
+                    // every store instruction touch 32 different lines and crowd the load/store
+                    // unit the converters need.
+                    uint8_t *stg = tiles + OUT_STAGING_OFFSET + (warp - FIRST_EPI_WARP) * OUT_STAGING_WARP_BYTES;
+                    const int row_base = row - lane;
 #pragma unroll
-                    for (int v = 0; v < 16; ++v)
-                        dst[v] = make_uint4(out[4 * v], out[4 * v + 1], out[4 * v + 2], out[4 * v + 3]);
-                } else {
+                    for (int ch = 0; ch < 2; ++ch) {
+                        if (lane == 0) bulk_wait_read_all();  // the previous box has left the buffer
+                        __syncwarp();
 #pragma unroll
-                    for (int j = 0; j < 64; ++j)
-                        if (col0 + j < args.M)
-                            crow[static_cast<long long>(col0 + j) * args.c_sj] = static_cast<int32_t>(out[j]);
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<uint4 *>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                                make_uint4(out[ch * 32 + 4 * c], out[ch * 32 + 4 * c + 1], out[ch * 32 + 4 * c + 2],
+                                           out[ch * 32 + 4 * c + 3]);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        const int gcol = col0 + ch * 32;
+                        if (lane == 0 && row_base < args.N && gcol < args.M) {
+                            tma_store_3d(&args.tmap_c, stg, gcol, row_base, b * args.c_batch_mul);
+                            bulk_commit_group();
+                        }
+                    }
+                } else if (row < args.N) {
+                    if (vec_ok && col0 + 64 <= args.M) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(crow + col0);
+#pragma unroll
+                        for (int v = 0; v < 16; ++v)
+                            dst[v] = make_uint4(out[4 * v], out[4 * v + 1], out[4 * v + 2], out[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 64; ++j)
+                            if (col0 + j < args.M)
+                                crow[static_cast<long long>(col0 + j) * args.c_sj] = static_cast<int32_t>(out[j]);
+                    }
                 }
             }
             acc_phase ^= 1u;
         }
+        // Bulk tensor stores in flight read this CTA's shared memory: done before it is given up.
+        if (lane == 0) bulk_wait_all();
     } else if (warp >= FIRST_CONV_WARP) {
         // ------------------------------------------------------------ converters
         const int r = threadIdx.x - FIRST_CONV_WARP * 32;  // 0..127: the row (A) / column (B) this thread splits
@@ -497,6 +532,15 @@ int launch_i32_tcgen05(const Problem &p) {
                             &args.b_batch_mul, why, sizeof(why))) {
         set_error("tensor map: %s", why);
         return TTB_EUNSUPPORTED;
+    }
+    {
+        // C as a "K-major operand": inner dim = columns (unit stride), outer = rows.
+        const OperandView cv{p.c, p.N, p.M, p.B, p.c_si, p.c_sj, p.c_sb};
+        char cw[128] = "";
+        if (p.c_sb != 0 && classify_operand(cv, 4, cw, sizeof(cw)) == kMajorK &&
+            encode_operand_tmap(&args.tmap_c, cv, kMajorK, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, 32, 32, 32,
+                                &args.c_batch_mul, cw, sizeof(cw)) == 0)
+            args.c_tma = 1;
     }
     args.c = static_cast<int32_t *>(p.c);
     args.c_sb = p.c_sb;
