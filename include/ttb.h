@@ -260,7 +260,13 @@ TTB_API const char *ttb_variant_name(int variant);
  * "tc_profile" (1 = record wait-cycle counters, see ttb_tc_profile),
  * "streamk" (f32 tensor-core kernel: deal the K blocks of all tiles out evenly
  * over the SMs instead of whole tiles; -1 = when whole tiles would leave SMs
- * idle, default; 0 = never; 1 = whenever possible).
+ * idle, default; 0 = never; 1 = whenever possible),
+ * "int_tensor" (1, default: large TMA-eligible i32 products run on the int8
+ * tensor cores as ten byte-plane products, exact mod 2^32; 0 = always the
+ * CUDA-core kernel), "conv_columns_mb" (budget in MiB of conv2d's unrolled
+ * columns workspace, default 2048; larger batches are processed in groups),
+ * "tc_debug" (bit mask of timing / fault-handling experiments of the f32
+ * tensor-core kernel, test only: results are wrong or absent when set).
  * Returns TTB_EINVAL for an unknown key or value. */
 TTB_API int ttb_set_option(const char *key, int64_t value);
 TTB_API int64_t ttb_get_option(const char *key);

@@ -95,3 +95,22 @@ def test_integer_bias_and_backward_wrap(oracle):
     g = rng.integers(0, 256, y.shape).astype(np.uint8)
     _, _, gb = oracle.conv2d_backward(g, x, w, 1, 1)
     assert np.array_equal(gb, g.astype(np.uint64).sum(axis=(0, 2, 3)).astype(np.uint8))
+
+
+GOLDEN = __import__("pathlib").Path(__file__).resolve().parent / "golden" / "conv_golden.npz"
+
+
+def test_port_matches_golden_vectors(oracle):
+    """tests/golden/conv_golden.npz holds outputs of the reference's own CPU conv2d kernels
+    (made by tests/golden/make_golden_conv.py where the reference tree exists).  The C
+    restatement must reproduce them bit for bit, forward and backward, for every dtype, also
+    where oracle/_ref is absent."""
+    data = np.load(GOLDEN)
+    keys = sorted(k[:-5] for k in data.files if k.endswith("_geom"))
+    assert len(keys) == 24
+    for key in keys:
+        s, p = (int(v) for v in data[key + "_geom"])
+        x, w, bias = data[key + "_x"], data[key + "_w"], data[key + "_bias"]
+        assert np.array_equal(oracle.conv2d_forward(x, w, bias, s, p), data[key + "_y"]), key
+        gx, gw, _ = oracle.conv2d_backward(data[key + "_g"], x, w, s, p)
+        assert np.array_equal(gx, data[key + "_gx"]) and np.array_equal(gw, data[key + "_gw"]), key

@@ -123,7 +123,9 @@ struct alignas(64) TcArgs {
     int dbg;          // test / timing switches; results are wrong when set.  bit 0: converter moves no
                       // data; 1: no proxy fence; 2: converter loads but does not store; 3: hybrid split
                       // adds bf16(A).bf16(B) instead of the corrections (layout check); 4: the first
-                      // stage is never loaded (the bounded waits must run out and the kernel unwind)
+                      // stage is never loaded (the bounded waits must run out and the kernel unwind);
+                      // 5: the epilogue issues no global stores; 6: every unit gets no work (set-up and
+                      // tear-down only) -- both for timing experiments
     long long *prof;  // optional: per-CTA wait-cycle counters (kProfSlots each), see ttb_tc_profile
 };
 

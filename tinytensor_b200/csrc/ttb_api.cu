@@ -155,8 +155,9 @@ int sm_count(int device, int *out) {
 }
 
 // Stream-K workspace of the f32 tensor-core kernel: partial-sum slots and ready flags, one
-// set per (device, stream) so that launches on different streams never share one.  The
-// flags carry the launch number, so nothing has to be cleared between launches.
+// set per (device, stream) so that launches on different streams never share one.  A flag is
+// raised by the unit that wrote partial sums and lowered by the unit that read them, so every
+// flag is 0 again when a kernel ends and nothing has to be cleared between launches.
 int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags) {
     DeviceState *d;
     int rc = device_state(device, &d);
