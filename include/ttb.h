@@ -77,7 +77,8 @@ enum ttb_variant {
     TTB_VARIANT_DMMA_F64 = 3,     /* f64: FP64 tensor-core (DMMA) kernel */
     TTB_VARIANT_SIMT_SPLITK = 4,  /* SIMT with K split over CTAs + scratch reduce */
     TTB_VARIANT_TCGEN05_2CTA = 5, /* f32: tcgen05 cta_group::2 (CTA pairs) */
-    TTB_VARIANT_TCGEN05_I8LIMB = 6 /* i32: exact mod 2^32 from ten u8 x u8 tcgen05 products of byte planes */
+    TTB_VARIANT_TCGEN05_I8LIMB = 6, /* i32: exact mod 2^32 from ten u8 x u8 tcgen05 products of byte planes */
+    TTB_VARIANT_SIMT_SKINNY = 7   /* one dim <= 16: streaming CUDA-core kernels (reported only; not forceable) */
 };
 
 /* ---- the hot path -------------------------------------------------------

@@ -37,6 +37,7 @@ class Variant(enum.IntEnum):
     SIMT_SPLITK = 4
     TCGEN05_2CTA = 5
     TCGEN05_I8LIMB = 6
+    SIMT_SKINNY = 7
 
 
 class _View(ctypes.Structure):

@@ -71,7 +71,8 @@ long long *profile_ptr(int device);
 int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags);
 
 // Per-dtype launchers.  Each returns a ttb_status.
-int launch_simt(const Problem &p, bool allow_splitk);
+// allow_skinny: products with one tiny dim may take the streaming kernels (automatic dispatch).
+int launch_simt(const Problem &p, bool allow_splitk, bool allow_skinny = false);
 struct F32Options {
     int terms = 2;      // 2 = hybrid split (TF32 big.big + two bf16 correction products, default);
                         // 3 = classic 3xTF32; 1 = one TF32 pass (test only)

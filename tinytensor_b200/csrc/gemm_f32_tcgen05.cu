@@ -1148,7 +1148,7 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     const long long waves = (args.total_tiles + units - 1) / units;
     const double busy = static_cast<double>(args.total_tiles) / static_cast<double>(waves * units);
     // (a fix-up costs about as much as a few K blocks: only long-K tiles are worth cutting)
-    const bool sk_worth = (num_kb >= 64 && total_kb / units >= 32) || (sk_small && units > args.total_tiles);
+    const bool sk_worth = (num_kb >= 64 && total_kb / units >= 16) || (sk_small && units > args.total_tiles);
     const bool sk_possible = args.total_tiles > 0 && total_kb / units >= 4 && total_kb < 0x7FFFFFFFLL &&
                              args.total_tiles / units + 2 <= kMaxSegments;
     bool streamk = streamk_opt > 0 ? sk_possible : (streamk_opt < 0 && sk_possible && sk_worth && busy < 0.93);

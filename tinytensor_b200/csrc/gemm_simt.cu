@@ -336,16 +336,159 @@ int launch_tile(const Problem &p, int splits, void *scratch) {
     return TTB_OK;
 }
 
+#include "gemm_skinny.cuh"
+
 }  // namespace
 
 int workspace_get(int device, size_t bytes, void **out);
 
+namespace {
+
+// out^T = rhs^T . lhs^T: the same product with the roles of the two operands (and of the
+// output's dims) exchanged, so that a tiny N is handled by the kernels written for a tiny M.
+Problem transposed(const Problem &p) {
+    Problem t = p;
+    t.a = p.b;
+    t.a_sb = p.b_sb;
+    t.a_si = p.b_sj;
+    t.a_sk = p.b_sk;
+    t.b = p.a;
+    t.b_sb = p.a_sb;
+    t.b_sk = p.a_sk;
+    t.b_sj = p.a_si;
+    t.N = p.M;
+    t.M = p.N;
+    t.c_si = p.c_sj;
+    t.c_sj = p.c_si;
+    t.d_si = p.d_sj;
+    t.d_sj = p.d_si;
+    return t;
+}
+
+template <typename U>
+bool vec4_ok(const void *base, long long s_inner, long long s_a, long long s_b) {
+    return s_inner == 1 && (s_a & 3) == 0 && (s_b & 3) == 0 &&
+           reinterpret_cast<uintptr_t>(base) % alignof(skinny::Vec4T<U>) == 0;
+}
+
+// Streams a product with one tiny dim (see gemm_skinny.cuh).  Returns TTB_OK when it launched,
+// 1 when the shape or the strides are not for these kernels, or a negative status.
+template <typename T>
+int launch_skinny_typed(const Problem &p0, int sms) {
+    using A = typename AccOf<T>::type;
+    Problem p = p0;
+    if (p.N <= skinny::kMaxSmall && p.M > skinny::kMaxSmall && p.K > skinny::kMaxSmall) p = transposed(p0);
+    if (p.B > 65535) return 1;
+    SimtArgs a{};
+    a.a = p.a;
+    a.b = p.b;
+    a.c = p.c;
+    a.N = p.N;
+    a.K = p.K;
+    a.M = p.M;
+    a.a_sb = p.a_sb;
+    a.a_si = p.a_si;
+    a.a_sk = p.a_sk;
+    a.b_sb = p.b_sb;
+    a.b_sk = p.b_sk;
+    a.b_sj = p.b_sj;
+    a.c_sb = p.c_sb;
+    a.c_si = p.c_si;
+    a.c_sj = p.c_sj;
+    a.splits = 1;
+    a.k_per_split = p.K;
+    a.c_ss = 0;
+    a.ep = epilogue_of(p);
+    cudaError_t e;
+    if (p.K <= skinny::kMaxSmall && p.M >= 32) {
+        const long long gblocks = ((p.M + 3) / 4 + 255) / 256;
+        if (p.N > 0x7FFFFFFFLL || gblocks > 65535) return 1;
+        dim3 grid(static_cast<unsigned>(p.N), static_cast<unsigned>(gblocks), static_cast<unsigned>(p.B));
+        skinny::outer_kernel<T><<<grid, 256, 0, p.stream>>>(a, static_cast<int>(p.K),
+                                                            vec4_ok<T>(p.b, p.b_sj, p.b_sk, p.b_sb) ? 1 : 0,
+                                                            vec4_ok<T>(p.c, p.c_sj, p.c_si, p.c_sb) ? 1 : 0);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "outer_kernel launch");
+        note_launch(TTB_VARIANT_SIMT_SKINNY, 1);
+        return TTB_OK;
+    }
+    if (p.M > skinny::kMaxSmall || p.K < 64) return 1;
+    const size_t bs_bytes = static_cast<size_t>(p.M) * p.K * sizeof(A);
+    const int mc = static_cast<int>((p.M + 3) / 4 * 4);
+    if (p.a_sk == 1 && p.N >= 32 && bs_bytes <= 96 * 1024) {
+        auto kernel = mc == 4 ? skinny::row_dot_kernel<T, 4>
+                      : mc == 8 ? skinny::row_dot_kernel<T, 8>
+                      : mc == 12 ? skinny::row_dot_kernel<T, 12>
+                                 : skinny::row_dot_kernel<T, 16>;
+        if (bs_bytes > 48 * 1024) {
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(row_dot smem)");
+        }
+        long long groups = (p.N + 31) / 32;
+        const long long cap = (2LL * sms + p.B - 1) / p.B;  // about two CTAs of 32 warps per SM
+        if (groups > cap) groups = cap;
+        dim3 grid(static_cast<unsigned>(groups), static_cast<unsigned>(p.B));
+        kernel<<<grid, 1024, bs_bytes, p.stream>>>(a, static_cast<int>(p.M));
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "row_dot_kernel launch");
+        note_launch(TTB_VARIANT_SIMT_SKINNY, 1);
+        return TTB_OK;
+    }
+    if (p.a_si == 1 && p.N >= 128) {
+        const long long row_blocks = (p.N + 127) / 128;
+        long long splits = (2LL * sms + row_blocks * p.B - 1) / (row_blocks * p.B);
+        if (splits > p.K / 64) splits = p.K / 64;
+        if (splits > 65535) splits = 65535;
+        if (splits < 1) splits = 1;
+        void *scratch = nullptr;
+        if (splits > 1) {
+            int rc = workspace_get(p.device, static_cast<size_t>(splits) * p.B * p.N * p.M * sizeof(T), &scratch);
+            if (rc != TTB_OK) return rc;
+            a.splits = static_cast<int>(splits);
+            a.k_per_split = (p.K + splits - 1) / splits;
+            a.c = scratch;
+            a.c_sb = p.N * p.M;
+            a.c_si = p.M;
+            a.c_sj = 1;
+            a.c_ss = p.B * p.N * p.M;
+            a.ep = Epilogue{nullptr, 0, 0, 0, 0};
+        }
+        if (row_blocks > 0x7FFFFFFFLL) return 1;
+        dim3 grid(static_cast<unsigned>(row_blocks), static_cast<unsigned>(splits), static_cast<unsigned>(p.B));
+        auto kernel = mc == 4 ? skinny::col_stream_kernel<T, 4>
+                      : mc == 8 ? skinny::col_stream_kernel<T, 8>
+                      : mc == 12 ? skinny::col_stream_kernel<T, 12>
+                                 : skinny::col_stream_kernel<T, 16>;
+        kernel<<<grid, 128, 0, p.stream>>>(a, static_cast<int>(p.M));
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "col_stream_kernel launch");
+        if (splits > 1) {
+            const long long total = p.B * p.N * p.M;
+            const int blocks = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+            splitk_reduce_kernel<T><<<blocks, 256, 0, p.stream>>>(static_cast<const T *>(scratch), static_cast<T *>(p.c),
+                                                                  p.B, p.N, p.M, static_cast<int>(splits), p.c_sb,
+                                                                  p.c_si, p.c_sj, epilogue_of(p));
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return cuda_fail(e, "splitk_reduce_kernel launch");
+        }
+        note_launch(TTB_VARIANT_SIMT_SKINNY, splits > 1 ? 2 : 1);
+        return TTB_OK;
+    }
+    return 1;
+}
+
+}  // namespace
+
 // Chooses a tile from the output shape, and a K split when the output alone
 // cannot fill the GPU.
 template <typename T>
-int launch_simt_typed(const Problem &p, bool allow_splitk) {
+int launch_simt_typed(const Problem &p, bool allow_splitk, bool allow_skinny) {
     int sms = 148;
     sm_count(p.device, &sms);
+    if (allow_skinny) {
+        const int rc = launch_skinny_typed<T>(p, sms);
+        if (rc <= 0) return rc;  // launched, or failed; 1 = not a shape for the streaming kernels
+    }
     constexpr int BKs = sizeof(T) >= 8 ? 8 : 16;
     auto tiles = [&](long long bm, long long bn) {
         return ((p.N + bm - 1) / bm) * ((p.M + bn - 1) / bn) * p.B;
@@ -397,14 +540,14 @@ int launch_simt_typed(const Problem &p, bool allow_splitk) {
     return rc;
 }
 
-int launch_simt(const Problem &p, bool allow_splitk) {
+int launch_simt(const Problem &p, bool allow_splitk, bool allow_skinny) {
     switch (p.dtype) {
-        case TTB_U8: return launch_simt_typed<uint8_t>(p, allow_splitk);
-        case TTB_I16: return launch_simt_typed<int16_t>(p, allow_splitk);
-        case TTB_I32: return launch_simt_typed<int32_t>(p, allow_splitk);
-        case TTB_I64: return launch_simt_typed<int64_t>(p, allow_splitk);
-        case TTB_F32: return launch_simt_typed<float>(p, allow_splitk);
-        case TTB_F64: return launch_simt_typed<double>(p, allow_splitk);
+        case TTB_U8: return launch_simt_typed<uint8_t>(p, allow_splitk, allow_skinny);
+        case TTB_I16: return launch_simt_typed<int16_t>(p, allow_splitk, allow_skinny);
+        case TTB_I32: return launch_simt_typed<int32_t>(p, allow_splitk, allow_skinny);
+        case TTB_I64: return launch_simt_typed<int64_t>(p, allow_splitk, allow_skinny);
+        case TTB_F32: return launch_simt_typed<float>(p, allow_splitk, allow_skinny);
+        case TTB_F64: return launch_simt_typed<double>(p, allow_splitk, allow_skinny);
         default: set_error("unsupported dtype %d", p.dtype); return TTB_EDTYPE;
     }
 }

@@ -439,15 +439,19 @@ static int dispatch(const Problem &p) {
             // CTA pairs (256x256 tiles) halve shared-memory and L2 traffic per flop; they
             // pay off once the output is more than one 128-wide tile in both dims and there
             // are enough pair tiles to occupy a good part of the GPU.
+            // Fewer pair tiles are fine when K is long: stream-K then deals the K blocks out over
+            // all pairs (16 or more each).
             const long long pair_tiles = ((p.N + 255) / 256) * ((p.M + 255) / 256) * p.B;
-            const bool pair = g_opt.two_cta < 0 ? (p.N > 128 && p.M > 128 && pair_tiles >= 24) : g_opt.two_cta != 0;
+            const long long kb = (p.K + 31) / 32;
+            const bool enough = pair_tiles >= 24 || (g_opt.streamk != 0 && kb >= 64 && pair_tiles * kb / (d->sms / 2) >= 16);
+            const bool pair = g_opt.two_cta < 0 ? (p.N > 128 && p.M > 128 && enough) : g_opt.two_cta != 0;
             return launch_f32_tcgen05(p, f32_options(pair));
         }
-        return launch_simt(p, g_opt.splitk != 0);
+        return launch_simt(p, g_opt.splitk != 0, true);
     }
     if (p.dtype == TTB_F64) {
-        if (p.N > 16 && p.M > 16 && f64_dmma_eligible(p)) return launch_f64_dmma(p);
-        return launch_simt(p, g_opt.splitk != 0);
+        if (p.N > 16 && p.M > 16 && p.K > 16 && f64_dmma_eligible(p)) return launch_f64_dmma(p);
+        return launch_simt(p, g_opt.splitk != 0, true);
     }
     if (p.dtype == TTB_I32 && g_opt.int_tensor != 0) {
         // Ten int8 tensor-core products of byte planes beat the 32-bit multiply-add pipe once
@@ -456,7 +460,7 @@ static int dispatch(const Problem &p) {
                          static_cast<double>(p.N) * p.M * p.K * p.B >= 256.0 * 256.0 * 256.0;
         if (big && i32_tcgen05_eligible(p, why, sizeof(why))) return launch_i32_tcgen05(p);
     }
-    return launch_simt(p, g_opt.splitk != 0);
+    return launch_simt(p, g_opt.splitk != 0, true);
 }
 
 }  // namespace ttb
@@ -734,6 +738,7 @@ TTB_API const char *ttb_variant_name(int variant) {
         case TTB_VARIANT_SIMT_SPLITK: return "simt_splitk";
         case TTB_VARIANT_TCGEN05_2CTA: return "tcgen05_3xtf32_2cta";
         case TTB_VARIANT_TCGEN05_I8LIMB: return "tcgen05_i8_byte_planes";
+        case TTB_VARIANT_SIMT_SKINNY: return "simt_skinny";
         default: return "unknown";
     }
 }
