@@ -266,6 +266,9 @@ TTB_API const char *ttb_variant_name(int variant);
  * tensor cores as ten byte-plane products, exact mod 2^32; 0 = always the
  * CUDA-core kernel), "conv_columns_mb" (budget in MiB of conv2d's unrolled
  * columns workspace, default 2048; larger batches are processed in groups),
+ * "peer_tma" (1, default: ttb_matmul_allgather reaches the peers with bulk
+ * tensor stores issued by the epilogue; 0: dedicated warps copy finished tiles
+ * with st.global),
  * "tc_debug" (bit mask of timing / fault-handling experiments of the f32
  * tensor-core kernel, test only: results are wrong or absent when set).
  * Returns TTB_EINVAL for an unknown key or value. */

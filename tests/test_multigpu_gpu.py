@@ -57,6 +57,14 @@ def _worker(rank, world, port, q):
             results[f"{name}_nccl"] = close(plain(A, B))
             # both exchanges deliver the same shards: bit-equal to each other
             results[f"{name}_fused_eq_nccl"] = bool(torch.equal(fused(A, B, out=C), plain(A, B)))
+            # the other way to reach the peers: forwarding warps instead of the epilogue's bulk
+            # tensor stores
+            ttb.set_option("peer_tma", 0)
+            C.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            results[f"{name}_fused_forwarding_warps_eq_nccl"] = bool(torch.equal(fused(A, B, out=C), plain(A, B)))
+            ttb.set_option("peer_tma", 1)
         # column blocks, integer dtype: goes through the NCCL exchange, bit-exact
         Ai = torch.randint(-8, 9, (1, 300, 128), generator=g, device=dev, dtype=torch.int32)
         Bi = torch.randint(-8, 9, (1, 128, 512), generator=g, device=dev, dtype=torch.int32)

@@ -81,6 +81,7 @@ struct F32Options {
     int mask_big = 0;   // converters also rewrite the raw tile with its masked big part (test only)
     int dbg = 0;        // timing experiments (wrong results when non-zero)
     int streamk = -1;   // K blocks dealt out evenly over the SMs: -1 automatic, 0 never, 1 whenever possible
+    int peer_tma = 1;   // fused all-gather: peers are reached by the epilogue's bulk tensor stores when possible
 };
 // n_peers > 0 fuses an all-gather into the product: every finished tile is also stored into
 // peer_c[i] (peer-mapped pointers to the other GPUs' C, same layout as p.c).

@@ -100,6 +100,7 @@ struct alignas(64) TcArgs {
     CUtensorMap tmap_a;
     CUtensorMap tmap_b;
     CUtensorMap tmap_c;  // C as {M, N, B} with 32 x 32 boxes, for the epilogue's bulk tensor stores
+    CUtensorMap tmap_peer[kMaxPeers];  // the same view of every peer GPU's C (fused all-gather)
     int c_tma;           // tmap_c is valid (C rows contiguous and 16-byte aligned)
     int c_batch_mul;     // 0 pins the batch coordinate (B == 1)
     float *c;
@@ -118,6 +119,8 @@ struct alignas(64) TcArgs {
     float *sk_partials;       // stream-K workspace: per unit, CTA and epilogue warp 32 x 128 partial sums
     unsigned int *sk_flags;   // stream-K flags, one per unit, CTA and epilogue warp: 1 while partial sums wait
     int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
+    int peer_tma;  // 1: the epilogue sends every box to the peers itself with bulk tensor stores
+                   // (tmap_peer); 0: the forwarding warps copy finished tiles with st.global
     float *peer_c[kMaxPeers];  // their C, laid out exactly like `c` (same offset and strides)
     DeviceStatus *status;
     int dbg;          // test / timing switches; results are wrong when set.  bit 0: converter moves no
@@ -356,6 +359,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 
     const int num_kb = (args.K + BK - 1) / BK;
     const int k_chunk = args.k_chunk > 0 ? args.k_chunk : num_kb;
+    // Peers served by the forwarding warps (none when the epilogue's tensor stores reach them).
+    const int fwd_peers = args.peer_tma ? 0 : args.n_peers;
     const int unit = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
     const int units = PAIR ? (gridDim.x >> 1) : gridDim.x;
     // This unit's segments.  n_store of them store C (all of them with whole tiles); the fused
@@ -599,7 +604,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 args.prof[blockIdx.x * kProfSlots + kProfMmaConv] = w_b;
             }
         }
-      } else if (args.n_peers > 0) {
+      } else if (fwd_peers > 0) {
         // ------------------------------------------------------------ forwarding (warps 2-3)
         // All-gather fused into the product: once the epilogue has stored a tile into this
         // GPU's C, these two warps read it back (it is still in L2) and store it into the same
@@ -762,7 +767,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             ++stored;
             const int row = tm * C::TILE_M + static_cast<int>(cta_rank) * BM + quarter * 32 + lane;
             const int col0 = tn * C::TILE_N + col_half * 128;
-            if (args.n_peers > 0) {
+            if (fwd_peers > 0) {
                 // The forwarding warps must be done with the tile that last used this slot.
                 if (!wait_or_abort<false>(&out_empty_bar[oslot], ophase ^ 1u, abort_flag)) {
                     if (lane == 0) report(args.status, abort_flag, kErrForwardWait, static_cast<unsigned>(oslot));
@@ -802,7 +807,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 #pragma unroll
                     for (int j = 0; j < 128; ++j) sum[j] = sum[j] < 0.0f ? 0.0f : sum[j];
                 }
-                if (args.c_tma && args.n_peers == 0) {
+                if (args.c_tma && fwd_peers == 0) {
                     // Row-contiguous, 16-byte-aligned C: each warp passes 32 columns at a time
                     // through its 4 KiB of shared memory, written in the 128-byte-swizzled layout
                     // (16-byte chunk XOR row) of a 32 x 32 TMA box, and one lane issues a bulk
@@ -825,6 +830,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                         const int gcol = col0 + ch * 32;
                         if (lane == 0 && row_base < args.N && gcol < args.M && !(args.dbg & 32)) {
                             tma_store_3d(&args.tmap_c, stg, gcol, row_base, b * args.c_batch_mul);
+                            // Fused all-gather: the same box goes to the same place of every
+                            // peer GPU's C over NVLink, straight from the staging buffer.
+                            for (int pr = 0; pr < args.n_peers; ++pr)
+                                tma_store_3d(&args.tmap_peer[pr], stg, gcol, row_base, b * args.c_batch_mul);
                             bulk_commit_group();
                         }
                     }
@@ -870,7 +879,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                         if (col0 + j < args.M) crow[static_cast<long long>(col0 + j) * args.c_sj] = sum[j];
                 }
             }
-            if (args.n_peers > 0) {
+            if (fwd_peers > 0) {
                 // Publish the tile (now in this GPU's C) to the forwarding warps.
                 __threadfence();
                 __syncwarp();
@@ -887,7 +896,11 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         }
         // Bulk tensor stores still in flight read this CTA's shared memory: they must be done
         // before the CTA gives it up.
-        if (lane == 0) bulk_wait_all();
+        if (lane == 0) {
+            bulk_wait_all();
+            // stores to peer GPUs must have left this GPU before the kernel is reported complete
+            if (args.n_peers > 0) __threadfence_system();
+        }
         if (args.prof && warp == C::FIRST_EPI_WARP && lane == 0) {
             args.prof[blockIdx.x * kProfSlots + kProfEpiAccFull] = w_a;
             args.prof[blockIdx.x * kProfSlots + kProfTotal] = clock64() - kernel_t0;
@@ -1034,7 +1047,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     // ---------------------------------------------------------------- fused all-gather, last tile
     // Every warp is done with its role by the time it gets here; the CTA's last tile has no
     // further math to hide behind, so all of them forward it.
-    if (args.n_peers > 0 && n_store > 0) {
+    if (fwd_peers > 0 && n_store > 0) {
         if (wait_or_abort<false>(&last_full_bar, 0u, abort_flag)) {
             forward_tile<CG>(args, last_store_tile, static_cast<int>(cta_rank), threadIdx.x, C::NUM_THREADS);
         } else if (threadIdx.x == 0) {
@@ -1223,6 +1236,21 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
     }
     args.n_peers = n_peers;
     for (int i = 0; i < n_peers; ++i) args.peer_c[i] = static_cast<float *>(peer_c[i]);
+    // When C can be described to TMA here and on every peer, the epilogue sends each box to the
+    // peers itself (bulk tensor stores from its staging buffer); otherwise the forwarding warps do.
+    args.peer_tma = 0;
+    if (n_peers > 0 && args.c_tma && opt.peer_tma) {
+        args.peer_tma = 1;
+        for (int i = 0; i < n_peers && args.peer_tma; ++i) {
+            const OperandView pv{peer_c[i], p.N, p.M, p.B, p.c_si, p.c_sj, p.c_sb};
+            char pw[128] = "";
+            int mul = 0;
+            if (classify_operand(pv, 4, pw, sizeof(pw)) != kMajorK ||
+                encode_operand_tmap(&args.tmap_peer[i], pv, kMajorK, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, 32, 32, 32, &mul,
+                                    pw, sizeof(pw)) != 0)
+                args.peer_tma = 0;
+        }
+    }
     int rc = device_status_ptr(p.device, &args.status);
     if (rc != TTB_OK) return rc;
     args.prof = profile_ptr(p.device);

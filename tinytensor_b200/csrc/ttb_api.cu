@@ -36,6 +36,7 @@ struct Options {
     int tc_debug = 0;
     int conv_columns_mb = 2048;  // budget of conv2d's unrolled-columns workspace
     int int_tensor = 1;          // i32 products may use the int8 tensor-core kernel
+    int peer_tma = 1;            // fused all-gather: epilogue tensor stores reach the peers (0: forwarding warps)
 };
 Options g_opt;
 
@@ -379,6 +380,7 @@ static F32Options f32_options(bool two_cta) {
     o.mask_big = g_opt.mask_big;
     o.dbg = g_opt.tc_debug;
     o.streamk = g_opt.streamk;
+    o.peer_tma = g_opt.peer_tma;
     return o;
 }
 
@@ -808,6 +810,10 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         g_opt.int_tensor = value != 0;
         return TTB_OK;
     }
+    if (!strcmp(key, "peer_tma")) {
+        g_opt.peer_tma = value != 0;
+        return TTB_OK;
+    }
     if (!strcmp(key, "conv_columns_mb")) {
         if (value < 1 || value > 65536) {
             set_error("conv_columns_mb must be 1..65536");
@@ -832,6 +838,7 @@ TTB_API int64_t ttb_get_option(const char *key) {
     if (!strcmp(key, "streamk")) return g_opt.streamk;
     if (!strcmp(key, "conv_columns_mb")) return g_opt.conv_columns_mb;
     if (!strcmp(key, "int_tensor")) return g_opt.int_tensor;
+    if (!strcmp(key, "peer_tma")) return g_opt.peer_tma;
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
