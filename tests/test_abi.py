@@ -117,3 +117,41 @@ def test_missing_library_fails_loudly(ttb, monkeypatch, tmp_path):
     monkeypatch.setattr(backend, "_lib", None)
     with pytest.raises(ttb.TTBError):
         backend.lib()
+
+
+def test_conv2d_and_fused_argument_checks_need_no_gpu(ttb):
+    """Shape, dtype and limit errors of the conv2d and fused entry points are found on the host,
+    before any CUDA call: they come back as status codes with a message (the tinytensor-side
+    adapter turns them into TTException)."""
+    from tinytensor_b200.backend import _ConvDesc, _View
+
+    L = ttb.lib()
+    one = ctypes.c_void_p(64)  # never dereferenced: every call below fails validation first
+
+    def conv(desc, dtype=5):
+        return L.ttb_conv2d_forward(one, one, None, one, ctypes.byref(desc), dtype, 0, None)
+
+    assert conv(_ConvDesc(1, 3, 8, 8, 4, 9, 1, 0)) == -2          # kernel larger than the image: TTB_ESHAPE
+    assert b"does not fit" in L.ttb_last_error()
+    assert conv(_ConvDesc(1, 3, 8, 8, 4, 3, 0, 0)) == -2          # stride 0
+    assert conv(_ConvDesc(1, 3, 8, 8, 4, 3, 1, -1)) == -2         # negative padding
+    assert conv(_ConvDesc(1, 3, 8, 8, 4, 3, 1, 0), dtype=0) == -3  # bool8: TTB_EDTYPE
+    assert conv(_ConvDesc(1, 70000, 8, 8, 4, 3, 1, 0)) == -9       # more than 65535 channels: TTB_ELIMIT
+    assert conv(_ConvDesc(4096, 64, 512, 512, 64, 3, 1, 1)) == -9  # beyond the reference's int indexing
+    assert L.ttb_conv2d_forward(one, one, None, one, None, 5, 0, None) == -1  # null description
+    assert L.ttb_conv2d_backward(one, one, one, one, None, None, ctypes.byref(_ConvDesc(1, 3, 8, 8, 4, 3, 1, 0)), 5,
+                                 0, None) == -1                    # null grad_weight
+
+    def view(shape, stride=None):
+        stride = stride or (shape[1] * shape[2], shape[2], 1)
+        return _View(ctypes.c_void_p(64), 0, (ctypes.c_int64 * 3)(*shape), (ctypes.c_int64 * 3)(*stride))
+
+    a, b = view((2, 8, 4)), view((2, 4, 6))
+    fused = lambda addend, act, dtype=5: L.ttb_batched_matmul_fused(
+        ctypes.byref(a), ctypes.byref(b), one, 0, None, ctypes.byref(addend) if addend is not None else None, act, dtype,
+        0, None)
+    assert fused(view((2, 8, 7)), 0) == -2                        # addend shape
+    assert b"addend" in L.ttb_last_error()
+    assert fused(None, 5) == -1                                   # unknown activation
+    assert fused(None, 1, dtype=3) == -3                          # relu on i32
+    assert fused(view((2, 8, 6), (48, 6, -1)), 0) == -1           # negative stride in the addend
