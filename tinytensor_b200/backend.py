@@ -467,6 +467,32 @@ def matmul(lhs: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
                    "(LHS=1, RHS=2), (LHS=2, RHS=1), (LHS=2, RHS=2) or (LHS=3, RHS=3).")
 
 
+def matmul_backward(lhs: torch.Tensor, rhs: torch.Tensor, grad_output: torch.Tensor):
+    """Gradients of ``matmul(lhs, rhs)`` as tinytensor's autograd computes them: the rank
+    plumbing of tensor.cpp:2403-2472 undone around TensorBatchedMatmul::backward
+    (autograd/binary_ops.cpp:172-179), i.e. two more products on PERMUTED VIEWS,
+    ``grad . rhs^T`` and ``lhs^T . grad``, which go to the kernels uncopied.
+    -> (grad_lhs, grad_rhs), shaped like the operands."""
+    ld, rd = lhs.dim(), rhs.dim()
+    if (ld, rd) == (1, 1):
+        l3, r3, g3 = lhs.reshape(1, 1, -1), rhs.reshape(1, -1, 1), grad_output.reshape(1, 1, 1)
+    elif (ld, rd) == (1, 2):
+        l3, r3, g3 = lhs.reshape(1, 1, -1), rhs.unsqueeze(0), grad_output.reshape(1, 1, -1)
+    elif (ld, rd) == (2, 1):
+        l3, r3, g3 = lhs.unsqueeze(0), rhs.reshape(1, -1, 1), grad_output.reshape(1, -1, 1)
+    elif (ld, rd) == (2, 2):
+        l3, r3, g3 = lhs.unsqueeze(0), rhs.unsqueeze(0), grad_output.unsqueeze(0)
+    elif (ld, rd) == (3, 3):
+        l3, r3, g3 = lhs, rhs, grad_output
+    else:
+        raise TTBError("Unsupported sizes. Try reshaping or broadcasting.")
+    if tuple(g3.shape) != (l3.shape[0], l3.shape[1], r3.shape[2]):
+        raise TTBError(f"grad_output has shape {tuple(grad_output.shape)}, which is not the shape of matmul(lhs, rhs)")
+    grad_l = batched_matmul(g3, r3.permute(0, 2, 1))
+    grad_r = batched_matmul(l3.permute(0, 2, 1), g3)
+    return grad_l.reshape(lhs.shape), grad_r.reshape(rhs.shape)
+
+
 def _np_view(a: np.ndarray) -> _View:
     if a.ndim != 3:
         raise TTBError(f"expected a rank-3 array, got rank {a.ndim}")
