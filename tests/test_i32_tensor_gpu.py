@@ -14,9 +14,11 @@ from gpu_util import dev, host
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture
-def forced(ttb, reset_options):
+@pytest.fixture(params=["cta", "pair"])
+def forced(ttb, reset_options, request):
+    """Both forms of the kernel: one CTA per 128 x 128 tile, and CTA pairs on 256 x 128 tiles."""
     ttb.set_option("force_variant", int(ttb.Variant.TCGEN05_I8LIMB))
+    ttb.set_option("two_cta", 0 if request.param == "cta" else 1)
     return ttb
 
 

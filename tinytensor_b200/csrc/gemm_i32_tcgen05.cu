@@ -13,7 +13,11 @@
 // Bit-exact for every input, any K.  Ten int8 MMAs (at twice the bf16 rate) replace the
 // 32-bit multiply-adds of the CUDA-core kernel.
 //
-// One CTA per SM, persistent over 128 x 128 tiles, roles by warp:
+// Two forms.  CG = 1: one CTA per SM, persistent over 128 x 128 tiles.  CG = 2: CTA pairs
+// (cta_group::2) over 256 x 128 tiles: each CTA loads and splits 128 rows of A and 64 columns
+// of B and owns 128 rows of the four accumulators; the pair's MMAs read both halves of B, so a
+// CTA moves a quarter less through shared memory per product (the binding resource).  Roles by
+// warp (in each CTA; only the leader CTA of a pair issues MMAs):
 //   warp 0       TMA producer: raw int32 tiles of A and B (32 K-elements = 128 bytes per row),
 //                through the same stride-derived tensor maps as the f32 kernel, so permuted
 //                views need no copy;
@@ -58,6 +62,7 @@ constexpr int EPI_WARPS = 8;           // two per TMEM lane quarter: each takes 
 constexpr int FIRST_EPI_WARP = 4, FIRST_CONV_WARP = FIRST_EPI_WARP + EPI_WARPS, NUM_CONV_WARPS = 4;
 constexpr int NUM_THREADS = (FIRST_CONV_WARP + NUM_CONV_WARPS) * 32;
 constexpr int TMEM_COLS = 512;        // P_0 .. P_3, 128 columns each
+constexpr int BN = 128;               // columns of B per tile (split over the CTAs of a pair)
 
 struct alignas(64) I8Args {
     CUtensorMap tmap_a;
@@ -118,6 +123,20 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = in_g / gsz;
 }
 
+// D[tmem] (+)= A * B with 8-bit integer inputs over a CTA pair (cta_group::2).
+__device__ __forceinline__ void mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "setp.ne.b32 P, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, P;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
@@ -135,20 +154,28 @@ __device__ __forceinline__ void planes_of(uint32_t w0, uint32_t w1, uint32_t w2,
     p3 = prmt(hi01, hi23, 0x7632);
 }
 
+template <int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __grid_constant__ I8Args args) {
+    constexpr bool PAIR = CG == 2;
+    constexpr int TILE_M = BM * CG;       // rows of C per CTA (pair)
+    constexpr int B_COLS = BN / CG;       // columns of B this CTA loads and splits
+    constexpr int B_RAW_BYTES = B_COLS * BK * 4;
+    constexpr int B_PLANE_BYTES = B_COLS * BK;
     extern __shared__ uint8_t smem_dyn[];
     __shared__ uint64_t full_bar[RAW_STAGES];     // TMA bytes landed
     __shared__ uint64_t empty_bar[RAW_STAGES];    // converters are done with the raw slot
-    __shared__ uint64_t plane_full_bar[PLANE_STAGES];   // byte planes written
-    __shared__ uint64_t plane_empty_bar[PLANE_STAGES];  // MMAs that read the plane slot are done
-    __shared__ uint64_t acc_full_bar;             // all K blocks of the tile accumulated
-    __shared__ uint64_t acc_empty_bar;            // accumulators read out
+    __shared__ uint64_t plane_full_bar[PLANE_STAGES];   // byte planes written (lives in the leader CTA)
+    __shared__ uint64_t plane_empty_bar[PLANE_STAGES];  // MMAs that read the plane slot are done (local)
+    __shared__ uint64_t acc_full_bar;             // all K blocks of the tile accumulated (local)
+    __shared__ uint64_t acc_empty_bar;            // accumulators read out (lives in the leader CTA)
     __shared__ uint64_t drain_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = cta_rank == 0;
     volatile int *abort_flag = &abort_flag_s;
     const uint32_t dyn_base = smem_u32(smem_dyn);
     const uint32_t tiles_base = (dyn_base + 1023u) & ~1023u;
@@ -160,11 +187,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
             mbar_init(&empty_bar[s], NUM_CONV_WARPS);
         }
         for (int s = 0; s < PLANE_STAGES; ++s) {
-            mbar_init(&plane_full_bar[s], NUM_CONV_WARPS);
+            mbar_init(&plane_full_bar[s], NUM_CONV_WARPS * CG);
             mbar_init(&plane_empty_bar[s], 1);
         }
         mbar_init(&acc_full_bar, 1);
-        mbar_init(&acc_empty_bar, EPI_WARPS);
+        mbar_init(&acc_empty_bar, EPI_WARPS * CG);
         mbar_init(&drain_bar, 1);
         abort_flag_s = 0;
         fence_mbar_init();
@@ -172,19 +199,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
         tma_prefetch_desc(&args.tmap_b);
     }
     if (warp == 1) {
-        tmem_alloc<1>(&tmem_base_slot, TMEM_COLS);
-        tmem_relinquish<1>();
+        tmem_alloc<CG>(&tmem_base_slot, TMEM_COLS);
+        tmem_relinquish<CG>();
     }
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) {
+        // The peer's barriers must be initialised before anything arrives on them.
+        cluster_arrive();
+        cluster_wait();
+    }
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
     const int num_kb = (args.K + BK - 1) / BK;
-    const int n_tiles = static_cast<int>(blockIdx.x) < args.total_tiles
-                            ? (args.total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                                  static_cast<int>(gridDim.x)
-                            : 0;
+    const int unit = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int units = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const int n_tiles = unit < args.total_tiles ? (args.total_tiles - unit + units - 1) / units : 0;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -195,9 +226,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
             int issued = 0;
             for (int i = 0; i < n_tiles && ok; ++i) {
                 int b, tm, tn;
-                tile_coords(static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x), args.tiles_m, args.tiles_n, b,
-                            tm, tn);
-                const int m0 = tm * BM, n0 = tn * BM;
+                tile_coords(unit + i * units, args.tiles_m, args.tiles_n, b, tm, tn);
+                const int m0 = tm * TILE_M + static_cast<int>(cta_rank) * BM;
+                const int n0 = tn * BN + static_cast<int>(cta_rank) * B_COLS;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!wait_or_abort(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         report(args.status, abort_flag, kErrProducerWait, static_cast<unsigned>(stage));
@@ -206,7 +237,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
                     }
                     uint8_t *a_dst = tiles + stage * STAGE_BYTES;
                     uint8_t *b_dst = a_dst + TILE_BYTES;
-                    mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+                    mbar_arrive_expect_tx(&full_bar[stage], TILE_BYTES + B_RAW_BYTES);
                     const int k0 = kb * BK;
                     if (args.a_mn_major) {
                         for (int j = 0; j < BM / 32; ++j)
@@ -216,7 +247,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
                         tma_load_3d(a_dst, &args.tmap_a, &full_bar[stage], k0, m0, b * args.a_batch_mul);
                     }
                     if (args.b_mn_major) {
-                        for (int j = 0; j < BM / 32; ++j)
+                        for (int j = 0; j < B_COLS / 32; ++j)
                             tma_load_3d(b_dst + j * MN_BOX_BYTES, &args.tmap_b, &full_bar[stage], n0 + 32 * j, k0,
                                         b * args.b_batch_mul);
                     } else {
@@ -240,8 +271,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc_u8(BM, BM);
+        if (lane == 0 && leader) {
+            const uint32_t idesc = make_idesc_u8(BM * CG, BN);
+            uint32_t peer_plane_empty[PLANE_STAGES] = {0, 0}, peer_acc_full = 0;
+            if constexpr (PAIR) {
+                for (int s = 0; s < PLANE_STAGES; ++s) peer_plane_empty[s] = mapa(smem_u32(&plane_empty_bar[s]), 1);
+                peer_acc_full = mapa(smem_u32(&acc_full_bar), 1);
+            }
             int ps = 0;
             uint32_t pphase = 0;
             uint32_t acc_phase = 0;
@@ -261,7 +297,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
                     }
                     tc_fence_after_sync();
                     // Plane tile: [K half][row][16 bytes]: core matrices (8 rows x 16 B) 128 B apart
-                    // along the rows (SBO), the two K halves 2048 B apart (LBO).
+                    // along the rows (SBO), the two K halves one half-tile apart (LBO): 2048 B for
+                    // the 128 rows of A, 16 B x this CTA's columns of B.
                     const uint32_t a_planes = tiles_base + PLANE_RING_OFFSET + ps * STAGE_BYTES;
                     const uint32_t b_planes = a_planes + 4 * PLANE_BYTES;
                     const uint32_t fresh = kb != 0 ? 1u : 0u;
@@ -270,24 +307,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
 #pragma unroll
                         for (int ia = 0; ia <= s; ++ia) {
                             const int ib = s - ia;
-                            mma_i8(tmem_base + static_cast<uint32_t>(s * BM),
-                                   make_smem_desc(a_planes + ia * PLANE_BYTES, 2048, 128, kSwizzleNone),
-                                   make_smem_desc(b_planes + ib * PLANE_BYTES, 2048, 128, kSwizzleNone), idesc,
-                                   ia == 0 ? fresh : 1u);
+                            const uint64_t da = make_smem_desc(a_planes + ia * PLANE_BYTES, 2048, 128, kSwizzleNone);
+                            const uint64_t db =
+                                make_smem_desc(b_planes + ib * B_PLANE_BYTES, B_COLS * 16, 128, kSwizzleNone);
+                            if constexpr (PAIR)
+                                mma_i8_pair(tmem_base + static_cast<uint32_t>(s * BN), da, db, idesc, ia == 0 ? fresh : 1u);
+                            else
+                                mma_i8(tmem_base + static_cast<uint32_t>(s * BN), da, db, idesc, ia == 0 ? fresh : 1u);
                         }
                     }
-                    mma_commit<1>(smem_u32(&plane_empty_bar[ps]));
+                    mma_commit<CG>(smem_u32(&plane_empty_bar[ps]));
+                    if constexpr (PAIR) mma_commit<CG>(peer_plane_empty[ps]);
                     if (++ps == PLANE_STAGES) {
                         ps = 0;
                         pphase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                mma_commit<1>(smem_u32(&acc_full_bar));
+                mma_commit<CG>(smem_u32(&acc_full_bar));
+                if constexpr (PAIR) mma_commit<CG>(peer_acc_full);
                 acc_phase ^= 1u;
             }
             // Everything issued must have retired before TMEM is freed.
-            mma_commit<1>(smem_u32(&drain_bar));
+            mma_commit<CG>(smem_u32(&drain_bar));
             for (int i = 0; i < 1000000; ++i)
                 if (mbar_try_wait(&drain_bar, 0)) break;
         }
@@ -297,19 +339,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
         const int col_half = (warp - FIRST_EPI_WARP) >> 2;  // columns [64 * col_half, +64) of the tile
         uint32_t acc_phase = 0;
         bool ok = true;
+        const uint32_t acc_empty_remote = PAIR ? mapa(smem_u32(&acc_empty_bar), 0) : 0u;
         const bool vec_ok = args.c_sj == 1 && (args.c_si & 3) == 0 && (args.c_sb & 3) == 0 &&
                             (reinterpret_cast<uintptr_t>(args.c) & 15) == 0;
         for (int i = 0; i < n_tiles && ok; ++i) {
             int b, tm, tn;
-            tile_coords(static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x), args.tiles_m, args.tiles_n, b, tm,
-                        tn);
+            tile_coords(unit + i * units, args.tiles_m, args.tiles_n, b, tm, tn);
             if (!wait_or_abort(&acc_full_bar, acc_phase, abort_flag)) {
                 if (lane == 0) report(args.status, abort_flag, kErrEpilogueWait, 0u);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            const int row = tm * BM + quarter * 32 + lane;
+            const int row = tm * TILE_M + static_cast<int>(cta_rank) * BM + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
             int32_t *crow = args.c + static_cast<long long>(b) * args.c_sb + static_cast<long long>(row) * args.c_si;
             const int32_t *drow = args.d ? args.d + static_cast<long long>(b) * args.d_sb +
@@ -323,18 +365,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 uint32_t p0[8], p1[8], p2[8], p3[8];
-                tmem_ld_32x8(t_col + static_cast<uint32_t>(0 * BM + q * 8), p0);
-                tmem_ld_32x8(t_col + static_cast<uint32_t>(1 * BM + q * 8), p1);
-                tmem_ld_32x8(t_col + static_cast<uint32_t>(2 * BM + q * 8), p2);
-                tmem_ld_32x8(t_col + static_cast<uint32_t>(3 * BM + q * 8), p3);
+                tmem_ld_32x8(t_col + static_cast<uint32_t>(0 * BN + q * 8), p0);
+                tmem_ld_32x8(t_col + static_cast<uint32_t>(1 * BN + q * 8), p1);
+                tmem_ld_32x8(t_col + static_cast<uint32_t>(2 * BN + q * 8), p2);
+                tmem_ld_32x8(t_col + static_cast<uint32_t>(3 * BN + q * 8), p3);
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 8; ++j) out[q * 8 + j] = p0[j] + (p1[j] << 8) + (p2[j] << 16) + (p3[j] << 24);
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty_bar);
-            const int col0 = tn * BM + col_half * 64;
+            if (lane == 0) {
+                if constexpr (PAIR)
+                    mbar_arrive_cluster(acc_empty_remote);
+                else
+                    mbar_arrive(&acc_empty_bar);
+            }
+            const int col0 = tn * BN + col_half * 64;
             if (col0 < args.M) {
                 if (drow && row < args.N) {
 #pragma unroll
@@ -388,7 +435,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
         if (lane == 0) bulk_wait_all();
     } else if (warp >= FIRST_CONV_WARP) {
         // ------------------------------------------------------------ converters
-        const int r = threadIdx.x - FIRST_CONV_WARP * 32;  // 0..127: the row (A) / column (B) this thread splits
+        const int r = threadIdx.x - FIRST_CONV_WARP * 32;  // 0..127: the row of A this thread splits
+        uint32_t plane_full_remote[PLANE_STAGES] = {0, 0};
+        if constexpr (PAIR) {
+            for (int s = 0; s < PLANE_STAGES; ++s) plane_full_remote[s] = mapa(smem_u32(&plane_full_bar[s]), 0);
+        }
         int stage = 0;
         uint32_t phase = 0;
         int ps = 0;
@@ -404,52 +455,59 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
             }
             const uint8_t *raw = tiles + stage * STAGE_BYTES;
             uint8_t *planes = tiles + PLANE_RING_OFFSET + ps * STAGE_BYTES;
+            // One work item = 16 consecutive K elements of one row (A) or column (B): four byte
+            // planes x 16 bytes.  A has 128 rows x 2 K halves; B has B_COLS columns x 2 K halves.
+            // Thread r takes both halves of A's row r and, for B, column (item % B_COLS) and half
+            // (item / B_COLS) of items r (and r + 128 when a CTA holds all 128 columns).
+            auto split = [&](const uint8_t *rt, uint8_t *pl, bool mn, int rr, int half, int lbo) {
+                uint32_t w[16];
+                if (!mn) {
+                    // K-major raw tile: 128-byte rows, 16-byte chunks XORed with (row & 7)
+                    const uint8_t *row = rt + rr * 128;
 #pragma unroll
-            for (int operand = 0; operand < 2; ++operand) {
-                const bool mn = operand ? (args.b_mn_major != 0) : (args.a_mn_major != 0);
-                const uint8_t *rt = raw + operand * TILE_BYTES;
-                uint8_t *pl = planes + operand * 4 * PLANE_BYTES;
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t w[16];
-                    if (!mn) {
-                        // K-major raw tile: 128-byte rows, 16-byte chunks XORed with (row & 7)
-                        const uint8_t *row = rt + r * 128;
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const uint4 v = *reinterpret_cast<const uint4 *>(row + (((half * 4 + c) ^ (r & 7)) << 4));
-                            w[4 * c] = v.x;
-                            w[4 * c + 1] = v.y;
-                            w[4 * c + 2] = v.z;
-                            w[4 * c + 3] = v.w;
-                        }
-                    } else {
-                        // MN-major raw tile: boxes of 32 (MN) x 32 (K); a K row is 128 bytes with
-                        // 32-byte chunks XORed with (k & 3)
-                        const uint8_t *box = rt + (r >> 5) * MN_BOX_BYTES + ((r & 7) << 2);
-                        const int chunk = (r & 31) >> 3;
-#pragma unroll
-                        for (int kk = 0; kk < 16; ++kk) {
-                            const int k = half * 16 + kk;
-                            w[kk] = *reinterpret_cast<const uint32_t *>(box + k * 128 + ((chunk ^ (k & 3)) << 5));
-                        }
+                    for (int c = 0; c < 4; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(row + (((half * 4 + c) ^ (rr & 7)) << 4));
+                        w[4 * c] = v.x;
+                        w[4 * c + 1] = v.y;
+                        w[4 * c + 2] = v.z;
+                        w[4 * c + 3] = v.w;
                     }
-                    uint4 q0, q1, q2, q3;
-                    planes_of(w[0], w[1], w[2], w[3], q0.x, q1.x, q2.x, q3.x);
-                    planes_of(w[4], w[5], w[6], w[7], q0.y, q1.y, q2.y, q3.y);
-                    planes_of(w[8], w[9], w[10], w[11], q0.z, q1.z, q2.z, q3.z);
-                    planes_of(w[12], w[13], w[14], w[15], q0.w, q1.w, q2.w, q3.w);
-                    uint8_t *dst = pl + half * 2048 + r * 16;
-                    *reinterpret_cast<uint4 *>(dst) = q0;
-                    *reinterpret_cast<uint4 *>(dst + PLANE_BYTES) = q1;
-                    *reinterpret_cast<uint4 *>(dst + 2 * PLANE_BYTES) = q2;
-                    *reinterpret_cast<uint4 *>(dst + 3 * PLANE_BYTES) = q3;
+                } else {
+                    // MN-major raw tile: boxes of 32 (MN) x 32 (K); a K row is 128 bytes with
+                    // 32-byte chunks XORed with (k & 3)
+                    const uint8_t *box = rt + (rr >> 5) * MN_BOX_BYTES + ((rr & 7) << 2);
+                    const int chunk = (rr & 31) >> 3;
+#pragma unroll
+                    for (int kk = 0; kk < 16; ++kk) {
+                        const int k = half * 16 + kk;
+                        w[kk] = *reinterpret_cast<const uint32_t *>(box + k * 128 + ((chunk ^ (k & 3)) << 5));
+                    }
                 }
-            }
+                uint4 q0, q1, q2, q3;
+                planes_of(w[0], w[1], w[2], w[3], q0.x, q1.x, q2.x, q3.x);
+                planes_of(w[4], w[5], w[6], w[7], q0.y, q1.y, q2.y, q3.y);
+                planes_of(w[8], w[9], w[10], w[11], q0.z, q1.z, q2.z, q3.z);
+                planes_of(w[12], w[13], w[14], w[15], q0.w, q1.w, q2.w, q3.w);
+                const int plane_bytes = lbo * 2;
+                uint8_t *dst = pl + half * lbo + rr * 16;
+                *reinterpret_cast<uint4 *>(dst) = q0;
+                *reinterpret_cast<uint4 *>(dst + plane_bytes) = q1;
+                *reinterpret_cast<uint4 *>(dst + 2 * plane_bytes) = q2;
+                *reinterpret_cast<uint4 *>(dst + 3 * plane_bytes) = q3;
+            };
+            const bool a_mn = args.a_mn_major != 0, b_mn = args.b_mn_major != 0;
+            split(raw, planes, a_mn, r, 0, 2048);
+            split(raw, planes, a_mn, r, 1, 2048);
+#pragma unroll
+            for (int item = r; item < 2 * B_COLS; item += 128)
+                split(raw + TILE_BYTES, planes + 4 * PLANE_BYTES, b_mn, item % B_COLS, item / B_COLS, B_COLS * 16);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&plane_full_bar[ps]);
+                if constexpr (PAIR)
+                    mbar_arrive_cluster(plane_full_remote[ps]);
+                else
+                    mbar_arrive(&plane_full_bar[ps]);
                 mbar_arrive(&empty_bar[stage]);
             }
             if (++stage == RAW_STAGES) {
@@ -467,10 +525,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
     // ---------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) {
+        // Neither CTA may leave while its peer can still signal its barriers or the pair's MMAs
+        // can still write its TMEM.
+        cluster_arrive();
+        cluster_wait();
+    }
     if (warp == 1) {
         __syncwarp();
         tc_fence_after_sync();
-        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+        tmem_dealloc<CG>(tmem_base, TMEM_COLS);
     }
 }
 
@@ -516,19 +580,18 @@ bool i32_tcgen05_eligible(const Problem &p, char *why, int why_len) {
     return plan(p, &pl, why, why_len);
 }
 
-int launch_i32_tcgen05(const Problem &p) {
-    I8Plan pl;
+namespace {
+
+template <int CG>
+int launch_i32_cg(const Problem &p, const I8Plan &pl) {
     char why[200] = "";
-    if (!plan(p, &pl, why, sizeof(why))) {
-        set_error("tcgen05 i32 kernel cannot take these views: %s", why);
-        return TTB_EUNSUPPORTED;
-    }
     I8Args args;
     memset(&args, 0, sizeof(args));
-    // The raw tiles are moved as 32-bit words; the same maps as the f32 kernel's.
+    // The raw tiles are moved as 32-bit words; the same maps as the f32 kernel's.  A K-major
+    // rhs is boxed by the columns one CTA loads (all 128, or 64 in a CTA pair).
     if (encode_operand_tmap(&args.tmap_a, pl.a, pl.a_major, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, 32, BM, BK,
                             &args.a_batch_mul, why, sizeof(why)) ||
-        encode_operand_tmap(&args.tmap_b, pl.b, pl.b_major, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, 32, BM, BK,
+        encode_operand_tmap(&args.tmap_b, pl.b, pl.b_major, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, 32, BN / CG, BK,
                             &args.b_batch_mul, why, sizeof(why))) {
         set_error("tensor map: %s", why);
         return TTB_EUNSUPPORTED;
@@ -556,26 +619,71 @@ int launch_i32_tcgen05(const Problem &p) {
     args.B = static_cast<int>(p.B);
     args.a_mn_major = pl.a_major == kMajorMN;
     args.b_mn_major = pl.b_major == kMajorMN;
-    args.tiles_m = static_cast<int>((p.N + BM - 1) / BM);
-    args.tiles_n = static_cast<int>((p.M + BM - 1) / BM);
+    args.tiles_m = static_cast<int>((p.N + BM * CG - 1) / (BM * CG));
+    args.tiles_n = static_cast<int>((p.M + BN - 1) / BN);
     args.total_tiles = args.tiles_m * args.tiles_n * args.B;
     int rc = device_status_ptr(p.device, &args.status);
     if (rc != TTB_OK) return rc;
+    auto kernel = gemm_i32_limb_kernel<CG>;
     static bool attr_set[64] = {false};
     if (!attr_set[p.device & 63]) {
-        cudaError_t e =
-            cudaFuncSetAttribute(gemm_i32_limb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
         attr_set[p.device & 63] = true;
     }
     int sms = 148;
     sm_count(p.device, &sms);
-    const int grid = sms < args.total_tiles ? sms : args.total_tiles;
-    gemm_i32_limb_kernel<<<grid, NUM_THREADS, SMEM_BYTES, p.stream>>>(args);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = p.stream;
+    cudaLaunchAttribute attr[1];
+    int units = sms / CG;  // CTAs, or CTA pairs, resident at once
+    if (CG == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        static int max_clusters[64] = {0};
+        if (max_clusters[p.device & 63] == 0) {
+            cfg.gridDim = dim3(static_cast<unsigned>(2 * units));
+            int n = 0;
+            cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveClusters");
+            if (n < 1) {
+                set_error("no CTA pair of the i32 tcgen05 kernel fits on device %d", p.device);
+                return TTB_ECUDA;
+            }
+            max_clusters[p.device & 63] = n;
+        }
+        if (units > max_clusters[p.device & 63]) units = max_clusters[p.device & 63];
+    }
+    if (units > args.total_tiles) units = args.total_tiles;
+    cfg.gridDim = dim3(static_cast<unsigned>(units * CG));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_i32_limb_kernel launch");
     note_launch(TTB_VARIANT_TCGEN05_I8LIMB, 1);
     return TTB_OK;
+}
+
+}  // namespace
+
+int launch_i32_tcgen05(const Problem &p, int two_cta) {
+    I8Plan pl;
+    char why[200] = "";
+    if (!plan(p, &pl, why, sizeof(why))) {
+        set_error("tcgen05 i32 kernel cannot take these views: %s", why);
+        return TTB_EUNSUPPORTED;
+    }
+    // CTA pairs (256 x 128 tiles) move a quarter less through shared memory per product; they
+    // need more than one 128-row tile of rows and enough pair tiles to occupy the GPU.
+    int sms = 148;
+    sm_count(p.device, &sms);
+    const long long pair_tiles = ((p.N + 255) / 256) * ((p.M + BN - 1) / BN) * p.B;
+    const bool pair = two_cta < 0 ? (p.N > 128 && pair_tiles >= sms / 4) : two_cta != 0;
+    return pair ? launch_i32_cg<2>(p, pl) : launch_i32_cg<1>(p, pl);
 }
 
 }  // namespace ttb
