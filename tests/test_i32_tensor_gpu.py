@@ -111,3 +111,22 @@ def test_ineligible_views_fall_back_to_cuda_cores(ttb, oracle, reset_options):
     got = host(ttb.batched_matmul(A, dev(b)))
     assert ttb.last_variant() in (ttb.Variant.SIMT, ttb.Variant.SIMT_SPLITK)
     assert np.array_equal(got, oracle.matmul(a[:, :, ::2], b))
+
+
+def test_wait_that_runs_out_is_reported_and_the_context_survives(forced, oracle):
+    """Failure detection without a GPU fault, as for the f32 kernel: a test switch makes the TMA
+    producer arm its first stage but never load it.  Every wait is bounded (2 s): the roles (in
+    both CTAs of a pair) give up, tensor memory is freed, the kernel returns, the host reads the
+    error word, and the next call on the same context is correct."""
+    rng = np.random.default_rng(76)
+    a, b = _full_range(rng, (1, 256, 64)), _full_range(rng, (1, 64, 256))
+    forced.check_device(0)
+    forced.set_option("tc_debug", 16)
+    forced.batched_matmul(dev(a), dev(b))
+    with pytest.raises(forced.TTBError) as info:
+        forced.check_device(0)
+    assert info.value.status == -6  # TTB_ETIMEOUT
+    forced.set_option("tc_debug", 0)
+    forced.check_device(0)
+    assert np.array_equal(host(forced.batched_matmul(dev(a), dev(b))), oracle.matmul(a, b))
+    forced.check_device(0)

@@ -88,7 +88,7 @@ struct F32Options {
 int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers = 0, void *const *peer_c = nullptr);
 bool f32_tcgen05_eligible(const Problem &p, char *why, int why_len);
 // two_cta: -1 = pick CTA pairs by shape, 0 = never, 1 = always.
-int launch_i32_tcgen05(const Problem &p, int two_cta = -1);
+int launch_i32_tcgen05(const Problem &p, int two_cta = -1, int dbg = 0);
 bool i32_tcgen05_eligible(const Problem &p, char *why, int why_len);
 int launch_f64_dmma(const Problem &p);
 bool f64_dmma_eligible(const Problem &p);

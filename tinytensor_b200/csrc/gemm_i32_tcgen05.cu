@@ -79,6 +79,8 @@ struct alignas(64) I8Args {
     int a_batch_mul, b_batch_mul;
     int tiles_m, tiles_n, total_tiles;
     DeviceStatus *status;
+    int dbg;  // test switch, bit 4: the first stage is armed but never loaded, so the bounded waits
+              // downstream must run out and the kernel unwind by itself (results are absent then)
 };
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -239,6 +241,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
                     uint8_t *b_dst = a_dst + TILE_BYTES;
                     mbar_arrive_expect_tx(&full_bar[stage], TILE_BYTES + B_RAW_BYTES);
                     const int k0 = kb * BK;
+                    if ((args.dbg & 16) && issued == 0) {
+                        ++issued;
+                        if (++stage == RAW_STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
                     if (args.a_mn_major) {
                         for (int j = 0; j < BM / 32; ++j)
                             tma_load_3d(a_dst + j * MN_BOX_BYTES, &args.tmap_a, &full_bar[stage], m0 + 32 * j, k0,
@@ -583,7 +593,7 @@ bool i32_tcgen05_eligible(const Problem &p, char *why, int why_len) {
 namespace {
 
 template <int CG>
-int launch_i32_cg(const Problem &p, const I8Plan &pl) {
+int launch_i32_cg(const Problem &p, const I8Plan &pl, int dbg) {
     char why[200] = "";
     I8Args args;
     memset(&args, 0, sizeof(args));
@@ -622,6 +632,7 @@ int launch_i32_cg(const Problem &p, const I8Plan &pl) {
     args.tiles_m = static_cast<int>((p.N + BM * CG - 1) / (BM * CG));
     args.tiles_n = static_cast<int>((p.M + BN - 1) / BN);
     args.total_tiles = args.tiles_m * args.tiles_n * args.B;
+    args.dbg = dbg;
     int rc = device_status_ptr(p.device, &args.status);
     if (rc != TTB_OK) return rc;
     auto kernel = gemm_i32_limb_kernel<CG>;
@@ -670,7 +681,7 @@ int launch_i32_cg(const Problem &p, const I8Plan &pl) {
 
 }  // namespace
 
-int launch_i32_tcgen05(const Problem &p, int two_cta) {
+int launch_i32_tcgen05(const Problem &p, int two_cta, int dbg) {
     I8Plan pl;
     char why[200] = "";
     if (!plan(p, &pl, why, sizeof(why))) {
@@ -683,7 +694,7 @@ int launch_i32_tcgen05(const Problem &p, int two_cta) {
     sm_count(p.device, &sms);
     const long long pair_tiles = ((p.N + 255) / 256) * ((p.M + BN - 1) / BN) * p.B;
     const bool pair = two_cta < 0 ? (p.N > 128 && pair_tiles >= sms / 4) : two_cta != 0;
-    return pair ? launch_i32_cg<2>(p, pl) : launch_i32_cg<1>(p, pl);
+    return pair ? launch_i32_cg<2>(p, pl, dbg) : launch_i32_cg<1>(p, pl, dbg);
 }
 
 }  // namespace ttb

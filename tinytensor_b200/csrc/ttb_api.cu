@@ -428,7 +428,7 @@ static int dispatch(const Problem &p) {
                 set_error("forced int8-plane tcgen05 variant cannot take this call: %s", why);
                 return TTB_EUNSUPPORTED;
             }
-            return launch_i32_tcgen05(p, g_opt.two_cta);
+            return launch_i32_tcgen05(p, g_opt.two_cta, g_opt.tc_debug);
         default: break;
     }
     // Automatic dispatch.
@@ -460,7 +460,7 @@ static int dispatch(const Problem &p) {
         // the 128 x 128 tiles are reasonably full and there is some K to amortise the epilogue.
         const bool big = p.N >= 64 && p.M >= 64 && p.K >= 64 &&
                          static_cast<double>(p.N) * p.M * p.K * p.B >= 256.0 * 256.0 * 256.0;
-        if (big && i32_tcgen05_eligible(p, why, sizeof(why))) return launch_i32_tcgen05(p, g_opt.two_cta);
+        if (big && i32_tcgen05_eligible(p, why, sizeof(why))) return launch_i32_tcgen05(p, g_opt.two_cta, g_opt.tc_debug);
     }
     return launch_simt(p, g_opt.splitk != 0, true);
 }
