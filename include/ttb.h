@@ -157,7 +157,10 @@ TTB_API int ttb_matmul_allgather(const ttb_view *lhs, const ttb_view *rhs, void 
  * makes the copies asynchronous).  Copies the operands' storage spans to the
  * device, runs ttb_batched_matmul on `device_id`, copies the contiguous result
  * back and synchronises.  Device staging buffers are cached per device and
- * grown on demand.  This is the call a CPU-resident caller makes, the
+ * grown on demand.  Large products are pipelined over three streams so that
+ * upload, product and download overlap: a single product (B == 1, rhs rows
+ * contiguous) in up to 8 blocks of output columns, a batched one (B >= 4,
+ * batch-major operands) in groups of batches.  This is the call a CPU-resident caller makes, the
  * equivalent of tinytensor's `matmul(a.to(cuda), b.to(cuda)).to(cpu)`
  * (autograd/unary_ops.cpp:67-83 + backend/cuda/matmul.cu:26-78). */
 TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, void *out,

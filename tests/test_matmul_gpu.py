@@ -203,15 +203,33 @@ def test_host_buffer_entry_point(ttb, oracle):
         check(got, a, b)
 
 
+def test_host_buffer_pipeline_rows(ttb):
+    """Products large enough to be pipelined through the host-buffer entry point, in blocks of
+    lhs rows (every copy one contiguous span), agree with the device-resident call: integers bit
+    for bit, f32 within the rounding of a different summation order.  lhs is a view into a wider
+    matrix (row pitch > K)."""
+    rng = np.random.default_rng(30)
+    for dt, (N, K, M) in ((np.int32, (5000, 2048, 2048)), (np.float32, (4200, 4096, 2048))):
+        wide, b = random_operands(rng, dt, 1, N, K + 72, M, -8, 9)
+        b = b[:, :K]
+        a = wide[:, :, 8:8 + K]
+        got = ttb.batched_matmul_host(a, b)
+        want = host(ttb.batched_matmul(dev(np.ascontiguousarray(a)), dev(np.ascontiguousarray(b))))
+        if dt == np.int32:
+            assert np.array_equal(got, want)
+        else:
+            assert rel_to_max(got, want) <= 2e-6
+
+
 def test_host_buffer_pipeline_columns(ttb):
-    """Products large enough to be pipelined in column blocks through the host-buffer entry
-    point agree with the device-resident call: integers bit for bit, f32 within the rounding of
-    a different summation order.  rhs is a view into a wider matrix (row pitch > M)."""
+    """The same in blocks of output columns, taken when the lhs rows are not contiguous (here the
+    lhs is stored transposed); rhs is a view into a wider matrix (row pitch > M)."""
     rng = np.random.default_rng(28)
     for dt, (N, K, M) in ((np.int32, (2048, 2048, 5000)), (np.float32, (2048, 4096, 4200))):
         a, wide = random_operands(rng, dt, 1, N, K, M + 72, -8, 9)
+        a_t = np.ascontiguousarray(a.transpose(0, 2, 1)).transpose(0, 2, 1)
         b = wide[:, :, 8:8 + M]
-        got = ttb.batched_matmul_host(a, b)
+        got = ttb.batched_matmul_host(a_t, b)
         want = host(ttb.batched_matmul(dev(a), dev(np.ascontiguousarray(b))))
         if dt == np.int32:
             assert np.array_equal(got, want)

@@ -254,3 +254,32 @@ def test_stream_k_distribution_matches_whole_tiles(forced, shape):
         assert np.array_equal(got, again), name  # fixed summation order: bit-repeatable
         first = got if first is None else first
     forced.check_device(0)
+
+
+def test_denormal_operands(forced):
+    """fp32 denormals (|x| < 2^-126).  The tensor cores do not flush them, but a denormal has no
+    full mantissa to split: its TF32 part keeps bits down to 2^-136 and the bf16 correction
+    cannot represent anything below 2^-133, so a denormal operand contributes with an ABSOLUTE
+    error of up to 2^-136 |b| per term instead of the relative 2^-22 of a normal one.
+    (a) Mixed into ordinary data that is far below everything else: the 1e-5 gate holds.
+    (b) A product whose every lhs entry is denormal: the error is bounded by that absolute
+        term (about 1e-2 of such a result), while the CUDA-core kernel keeps fp32 accuracy --
+        the documented deviation of the split-precision path."""
+    rng = np.random.default_rng(47)
+    K = 256
+    a = rng.standard_normal((1, 128, K)).astype(np.float32)
+    b = rng.standard_normal((1, K, 128)).astype(np.float32)
+    a[0, ::3, ::5] = (rng.standard_normal(a[0, ::3, ::5].shape) * 1e-39).astype(np.float32)
+    b[0, ::7, ::2] = (rng.standard_normal(b[0, ::7, ::2].shape) * 1e-40).astype(np.float32)
+    assert (np.abs(a[a != 0]).min() < 1.1754944e-38) and (np.abs(b[b != 0]).min() < 1.1754944e-38)
+    got = host(forced.batched_matmul(dev(a), dev(b)))
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    assert rel_to_max(got, want) <= F32_TOL
+    a = (rng.standard_normal((1, 128, K)) * 1e-39).astype(np.float32)
+    b = (rng.standard_normal((1, K, 128)) * 1e20).astype(np.float32)
+    got = host(forced.batched_matmul(dev(a), dev(b)))
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    assert np.count_nonzero(got) == got.size          # nothing was flushed to zero
+    bound = 2.0 ** -136 * np.abs(b).astype(np.float64).sum(axis=1).max()  # 2^-136 |b| per term, worst column
+    assert np.abs(got - want).max() <= bound
+    assert rel_to_max(got, want) <= 5e-2

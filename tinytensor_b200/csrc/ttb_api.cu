@@ -595,31 +595,39 @@ TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, vo
     // Large products are pipelined in chunks so that the upload of chunk j+1, the product of
     // chunk j and the download of chunk j-1 overlap (PCIe is full duplex, the copy engines
     // run beside the SMs):
-    //  * B == 1, rhs rows contiguous: chunks of output columns.  lhs goes up first, then the
-    //    column blocks of rhs (2-D copies); each block's product is written into its columns
-    //    of C and downloaded as soon as it is done.
+    //  * B == 1, lhs rows contiguous: chunks of output rows.  rhs goes up first, then blocks of
+    //    lhs rows; each block's product is a block of rows of C, downloaded as soon as it is
+    //    done.  Every copy is one contiguous span.
+    //  * B == 1, only rhs rows contiguous: chunks of output columns, the same with the roles
+    //    exchanged (the column blocks of rhs and C are 2-D copies).
     //  * B >= 4, batch-major operands: chunks of batches.
     // Anything else, and small products, take the plain path: copy, multiply, copy.
     const double work = 2.0 * static_cast<double>(p.B) * p.N * p.K * p.M;
     const int64_t a_one = (lhs->size[1] - 1) * lhs->stride[1] + (lhs->size[2] - 1) * lhs->stride[2] + 1;
     const int64_t b_one = (rhs->size[1] - 1) * rhs->stride[1] + (rhs->size[2] - 1) * rhs->stride[2] + 1;
-    const bool by_cols = p.B == 1 && rhs->stride[2] == 1 && rhs->stride[1] >= p.M && p.M >= 1024 && work >= 4e10;
-    const bool by_batch = !by_cols && p.B >= 4 && lhs->stride[0] >= a_one && rhs->stride[0] >= b_one &&
+    const bool by_rows = p.B == 1 && lhs->stride[2] == 1 && lhs->stride[1] >= p.K && p.N >= 1024 && work >= 4e10;
+    const bool by_cols = !by_rows && p.B == 1 && rhs->stride[2] == 1 && rhs->stride[1] >= p.M && p.M >= 1024 &&
+                         work >= 4e10;
+    const bool by_batch = !by_rows && !by_cols && p.B >= 4 && lhs->stride[0] >= a_one && rhs->stride[0] >= b_one &&
                           work >= 4e10;
-    if (by_cols || by_batch) {
+    if (by_rows || by_cols || by_batch) {
         rc = host_streams(d);
         if (rc != TTB_OK) return rc;
         cudaStream_t s_up = d->hs[0], s_mm = d->hs[1], s_down = d->hs[2];
-        const int64_t extent = by_cols ? p.M : p.B;
-        int nch = by_cols ? static_cast<int>(extent / 1024) : static_cast<int>(extent / 2);
+        const int64_t extent = by_rows ? p.N : by_cols ? p.M : p.B;
+        int nch = by_batch ? static_cast<int>(extent / 2) : static_cast<int>(extent / 1024);
         if (nch > kHostChunks) nch = kHostChunks;
         if (nch < 2) nch = 2;
-        // chunk edges: multiples of 128 columns / whole batches
-        const int64_t gran = by_cols ? 128 : 1;
+        // chunk edges: multiples of 128 rows or columns / whole batches
+        const int64_t gran = by_batch ? 1 : 128;
         const int64_t per = ((extent + nch - 1) / nch + gran - 1) / gran * gran;
         if (by_cols) {
             e = cudaMemcpyAsync(da, ha, a_bytes, cudaMemcpyHostToDevice, s_up);
             if (e != cudaSuccess) return cuda_fail(e, "H2D lhs");
+        }
+        if (by_rows) {
+            e = cudaMemcpyAsync(db, hb, b_bytes, cudaMemcpyHostToDevice, s_up);
+            if (e != cudaSuccess) return cuda_fail(e, "H2D rhs");
         }
         const Problem full = p;
         for (int c = 0; c < nch; ++c) {
@@ -627,7 +635,15 @@ TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, vo
             if (x0 >= extent) break;
             Problem q = full;
             q.stream = s_mm;
-            if (by_cols) {
+            if (by_rows) {
+                const size_t a_off = static_cast<size_t>(x0 * lhs->stride[1]) * es;
+                const size_t a_len = static_cast<size_t>((x1 - x0 - 1) * lhs->stride[1] + p.K) * es;
+                e = cudaMemcpyAsync(static_cast<char *>(da) + a_off, ha + a_off, a_len, cudaMemcpyHostToDevice, s_up);
+                if (e != cudaSuccess) return cuda_fail(e, "H2D lhs rows");
+                q.a = static_cast<char *>(da) + a_off;
+                q.c = static_cast<char *>(dc) + static_cast<size_t>(x0) * p.M * es;
+                q.N = x1 - x0;
+            } else if (by_cols) {
                 const size_t pitch = static_cast<size_t>(rhs->stride[1]) * es;
                 e = cudaMemcpy2DAsync(static_cast<char *>(db) + x0 * es, pitch, hb + x0 * es, pitch,
                                       static_cast<size_t>(x1 - x0) * es, static_cast<size_t>(p.K),
@@ -663,7 +679,11 @@ TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, vo
             if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
             e = cudaStreamWaitEvent(s_down, d->hev[2 * c + 1], 0);
             if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
-            if (by_cols) {
+            if (by_rows) {
+                const size_t off = static_cast<size_t>(x0) * p.M * es;
+                e = cudaMemcpyAsync(static_cast<char *>(out) + off, static_cast<char *>(dc) + off,
+                                    static_cast<size_t>(x1 - x0) * p.M * es, cudaMemcpyDeviceToHost, s_down);
+            } else if (by_cols) {
                 const size_t pitch = static_cast<size_t>(p.M) * es;
                 e = cudaMemcpy2DAsync(static_cast<char *>(out) + x0 * es, pitch, static_cast<char *>(dc) + x0 * es, pitch,
                                       static_cast<size_t>(x1 - x0) * es, static_cast<size_t>(p.N),
