@@ -115,7 +115,8 @@ struct alignas(64) TcArgs {
     int terms;     // 3 = split-TF32, 1 = single pass (test only)
     int k_chunk;   // K blocks per TMEM accumulation chunk
     int mask_big;  // converters also overwrite the raw tile with its masked big part
-    int streamk;   // 1: K blocks are dealt out evenly over the units (see Work), else whole tiles
+    int streamk;   // 1: K blocks are dealt out evenly over the units (see above), else whole tiles
+    int sk_tile0;  // stream-K: tiles [0, sk_tile0) stay whole; the rest is cut by K blocks
     float *sk_partials;       // stream-K workspace: per unit, CTA and epilogue warp 32 x 128 partial sums
     unsigned int *sk_flags;   // stream-K flags, one per unit, CTA and epilogue warp: 1 while partial sums wait
     int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
@@ -195,16 +196,18 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 
 // Work distribution over the resident units (CTAs, or CTA pairs).
 //  whole tiles: unit u takes tiles u, u + units, u + 2 units, ... with all of K.
-//  stream-K   : the tile-major sequence of all K blocks of all tiles is cut into `units` equal
-//               contiguous ranges, so every unit gets the same amount of work whatever the tile
-//               count.  A range falls into segments (tile, [kb0, kb1)), listed in shared memory
+//  stream-K   : the first sk_tile0 tiles (whole waves of tiles, a multiple of `units`) are dealt out
+//               whole as above and processed first; the tile-major sequence of all K blocks of
+//               the REMAINING tiles is cut into `units` equal contiguous ranges, so every unit
+//               gets the same amount of work whatever the tile count, and only the last partial
+//               wave pays for fix-ups (sk_tile0 == 0: every tile is cut that way).  A range falls into segments (tile, [kb0, kb1)), listed in shared memory
 //               at kernel start (at most kMaxSegments; the host only picks stream-K when that
 //               holds).  A segment with kb0 == 0 owns its tile: it stores C, after adding the
 //               partial sums of the units whose ranges start inside the tile.  A segment with
 //               kb0 > 0 (always the first of its range) writes its partial sums to a workspace
 //               and raises a flag.  Owners wait only for units that do that work first, so no
 //               wait is circular.
-constexpr int kMaxSegments = 16;
+constexpr int kMaxSegments = 32;
 
 // Fused all-gather: copies this CTA's 128 rows of tile `t` from this GPU's C (just written by
 // the epilogue, still in L2) into the same place of every peer's C.  `tid` of `nthreads`
@@ -322,15 +325,21 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             // cut this unit's K-block range into per-tile segments
             const int nkb = (args.K + BK - 1) / BK;
             const int u = PAIR ? (blockIdx.x >> 1) : blockIdx.x, us = PAIR ? (gridDim.x >> 1) : gridDim.x;
-            const long long all = static_cast<long long>(args.total_tiles) * nkb;  // < 2^31, checked by the host
+            int n = 0;
+            for (int t = u; t < args.sk_tile0 && n < kMaxSegments; t += us) {  // whole tiles first
+                seg_tile_s[n] = t;
+                seg_kb0_s[n] = 0;
+                seg_kb1_s[n] = nkb;
+                ++n;
+            }
+            const long long all = static_cast<long long>(args.total_tiles - args.sk_tile0) * nkb;  // < 2^31 (host)
             int pos = static_cast<int>(all * u / us);
             const int end = static_cast<int>(all * (u + 1) / us);
-            int n = 0;
             while (pos < end && n < kMaxSegments) {
-                const int tile = pos / nkb, k0 = pos - tile * nkb;
+                const int rel = pos / nkb, k0 = pos - rel * nkb;
                 int stop = pos + (nkb - k0);
                 if (stop > end) stop = end;
-                seg_tile_s[n] = tile;
+                seg_tile_s[n] = args.sk_tile0 + rel;
                 seg_kb0_s[n] = k0;
                 seg_kb1_s[n] = k0 + (stop - pos);
                 ++n;
@@ -723,9 +732,9 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             }
             if (kb1 != num_kb) {
                 // Stream-K, the owner of a tile whose tail other units computed: add their sums.
-                const long long all_kb = static_cast<long long>(args.total_tiles) * num_kb;
+                const long long all_kb = static_cast<long long>(args.total_tiles - args.sk_tile0) * num_kb;
                 for (int q = unit + 1; q < units && ok; ++q) {
-                    if (all_kb * q / units >= static_cast<long long>(t + 1) * num_kb) break;
+                    if (all_kb * q / units >= static_cast<long long>(t - args.sk_tile0 + 1) * num_kb) break;
                     const long long slot = (static_cast<long long>(q) * CG + cta_rank) * EPI_WARPS + epi_warp;
                     unsigned long long t0 = 0;
                     for (uint32_t spin = 0;; ++spin) {
@@ -1160,11 +1169,18 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     }
     const long long waves = (args.total_tiles + units - 1) / units;
     const double busy = static_cast<double>(args.total_tiles) / static_cast<double>(waves * units);
-    // (a fix-up costs about as much as a few K blocks: only long-K tiles are worth cutting)
-    const bool sk_worth = (num_kb >= 64 && total_kb / units >= 16) || (sk_small && units > args.total_tiles);
-    const bool sk_possible = args.total_tiles > 0 && total_kb / units >= 4 && total_kb < 0x7FFFFFFFLL &&
-                             args.total_tiles / units + 2 <= kMaxSegments;
+    const long long waves_full = args.total_tiles / units, rem = args.total_tiles % units;
+    // Whole waves of tiles stay whole; the K blocks of the last partial wave are dealt out over
+    // all units (with no whole wave: of every tile).  Each unit needs a few K blocks of that to
+    // be worth a fix-up.
+    const long long cut_tiles = waves_full > 0 ? rem : args.total_tiles;
+    const long long cut_kb_per_unit = cut_tiles * num_kb / units;
+    const bool sk_worth = waves_full > 0 ? cut_kb_per_unit >= 8
+                                         : ((num_kb >= 64 && cut_kb_per_unit >= 16) || (sk_small && units > args.total_tiles));
+    const bool sk_possible = cut_tiles > 0 && cut_kb_per_unit >= 4 && cut_tiles * num_kb < 0x7FFFFFFFLL &&
+                             waves_full + 3 <= kMaxSegments;
     bool streamk = streamk_opt > 0 ? sk_possible : (streamk_opt < 0 && sk_possible && sk_worth && busy < 0.93);
+    args.sk_tile0 = static_cast<int>(waves_full * units);
     if (streamk) {
         int rc = streamk_workspace(p.device, p.stream, &args.sk_partials, &args.sk_flags);
         if (rc != TTB_OK) streamk = false;  // no workspace for this stream: whole tiles
