@@ -217,14 +217,22 @@ def run_ours(args):
     std = DIM ** -0.5
     A = torch.randn((1, DIM, DIM), generator=g, device=dev) * std
     B = torch.randn((1, DIM, DIM), generator=g, device=dev) * std
-    sharded = ttb.ShardedMatmul() if world > 1 else None
-    if world > 1 and args.exchange == "fused":
+    fused = args.exchange in ("fused", "fused-peer", "fused-multicast")
+    sharded = ttb.ShardedMatmul(exchange={"fused": "peer", "fused-peer": "peer", "fused-multicast": "multicast"}.get(
+        args.exchange, "auto")) if world > 1 else None
+    if world > 1 and fused:
         # C in symmetric memory: the GEMM kernel itself stores each finished tile into every
         # rank's C over NVLink (fused all-gather); "nccl" keeps C private and all-gathers after.
         C = sharded.symmetric_output((1, DIM, DIM), torch.float32, dev)
     else:
         C = torch.empty((1, DIM, DIM), device=dev)
     part = ttb.partition(1, DIM, DIM, DIM, world, rank)
+    exchange_desc = "NCCL all_gather + re-layout"
+    if world > 1 and fused:
+        multicast = sharded.exchange != "peer" and getattr(sharded._symm[1], "has_multicast_support", False)
+        exchange_desc = ("fused into the GEMM kernel: each tile stored once through NVSwitch multicast (multimem.st)"
+                         if multicast else
+                         "fused into the GEMM kernel: bulk tensor stores from the epilogue to every peer over NVLink")
 
     def step():
         if sharded is None:
@@ -360,7 +368,7 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "parallelism": (f"column blocks x{world} + all-gather of C "
-                                       f"({'fused into the GEMM kernel, peer stores over NVLink' if args.exchange == 'fused' else 'NCCL all_gather + re-layout'})")
+                                       f"({exchange_desc})")
                        if world > 1 else "single GPU",
                        "l2": "operands (768 MiB with C) exceed the 126 MB L2; no explicit flush",
                        "kernel": variant, "arithmetic": ("split precision on tcgen05: TF32 product of the high parts + two bf16 "
@@ -390,7 +398,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--exchange", default="fused", choices=["fused", "fused-peer", "fused-multicast", "nccl"],
                     help="N > 1: how C is all-gathered (fused into the GEMM kernel, or NCCL after it)")
     ap.add_argument("--workload", default="c4", choices=["c1", "c2", "c3", "c4", "c4b", "c5", "conv", "linear"],
                     help="c4 (default) is the headline configuration; c1..c5 are the remaining "

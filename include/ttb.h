@@ -153,6 +153,21 @@ TTB_API int ttb_matmul_allgather(const ttb_view *lhs, const ttb_view *rhs, void 
                                  void *const *peer_out, int n_peers, int dtype,
                                  int device_id, void *stream);
 
+/* The same fused product + all-gather through NVSwitch multicast.  `multicast_out` is
+ * the multicast address of C: a virtual address bound (cuMulticastBindMem / a
+ * symmetric-memory allocator) to the C buffers of ALL participating GPUs, laid out like
+ * `out` (same out_offset and strides).  The kernel stores every finished tile once, with
+ * multimem.st, to that address; the switch delivers it to every GPU, this one included,
+ * so a GPU sends each byte of its block once instead of once per peer.  `out` (this
+ * GPU's own mapping of C) is only used to describe the layout.  Needs row-contiguous,
+ * 16-byte-aligned rows of C and a column count that is a multiple of 4; otherwise
+ * TTB_EUNSUPPORTED (use ttb_matmul_allgather).  Completion as there: kernel done on
+ * every rank, then a cross-rank barrier.  No counterpart in the reference. */
+TTB_API int ttb_matmul_allgather_multicast(const ttb_view *lhs, const ttb_view *rhs, void *out,
+                                           int64_t out_offset, const int64_t out_stride[3],
+                                           void *multicast_out, int dtype, int device_id,
+                                           void *stream);
+
 /* Host-buffer form: lhs/rhs `data` and `out` are HOST pointers (pinned memory
  * makes the copies asynchronous).  Copies the operands' storage spans to the
  * device, runs ttb_batched_matmul on `device_id`, copies the contiguous result

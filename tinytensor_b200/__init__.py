@@ -30,6 +30,7 @@ from .backend import (  # noqa: F401
     matmul,
     matmul_backward,
     matmul_allgather,
+    matmul_allgather_multicast,
     set_option,
     tma_eligible,
     view_of,
@@ -39,6 +40,6 @@ from .partition import Partition, ShardedMatmul, partition  # noqa: F401
 __all__ = [
     "Activation", "TTBError", "Variant", "batched_matmul", "batched_matmul_fused", "conv2d", "conv2d_backward", "linear", "batched_matmul_host", "batched_matmul_static_scratch",
     "check_device", "get_option",
-    "last_variant", "launch_count", "lib", "lib_path", "matmul", "matmul_allgather", "matmul_backward", "set_option", "tma_eligible",
+    "last_variant", "launch_count", "lib", "lib_path", "matmul", "matmul_allgather", "matmul_allgather_multicast", "matmul_backward", "set_option", "tma_eligible",
     "view_of", "Partition", "ShardedMatmul", "partition",
 ]

@@ -114,6 +114,10 @@ def lib() -> ctypes.CDLL:
         vp, vp, ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_void_p),
         ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
     L.ttb_matmul_allgather.restype = ctypes.c_int
+    L.ttb_matmul_allgather_multicast.argtypes = [
+        vp, vp, ctypes.c_void_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p, ctypes.c_int,
+        ctypes.c_int, ctypes.c_void_p]
+    L.ttb_matmul_allgather_multicast.restype = ctypes.c_int
     L.ttb_batched_matmul_static_scratch.argtypes = [vp, vp, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                                     ctypes.c_void_p]
     L.ttb_batched_matmul_static_scratch.restype = ctypes.c_int
@@ -390,6 +394,26 @@ def matmul_allgather(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor, pe
     rc = lib().ttb_matmul_allgather(ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.untyped_storage().data_ptr()),
                                 out.storage_offset(), strides, peers, len(peer_bases), _DTYPE_CODE[lhs.dtype], dev,
                                 ctypes.c_void_p(_stream_ptr(stream)))
+    if rc != 0:
+        _raise(rc)
+    return out
+
+
+def matmul_allgather_multicast(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor, multicast_base: int,
+                               stream=None) -> torch.Tensor:
+    """``ttb_matmul_allgather_multicast``: like matmul_allgather, but every finished tile is stored
+    once to the NVSwitch multicast address of C (`multicast_base`: the multicast pointer of the
+    symmetric buffer that holds `out`), which delivers it to every GPU."""
+    if lhs.dtype != torch.float32 or rhs.dtype != torch.float32 or out.dtype != torch.float32:
+        raise TTBError("matmul_allgather_multicast: f32 only")
+    if out.dim() != 3 or tuple(out.shape) != (lhs.shape[0], lhs.shape[1], rhs.shape[2]):
+        raise TTBError("matmul_allgather_multicast: out has the wrong shape")
+    dev = lhs.device.index if lhs.device.index is not None else torch.cuda.current_device()
+    lv, rv = view_of(lhs), view_of(rhs)
+    strides = (ctypes.c_int64 * 3)(*out.stride())
+    rc = lib().ttb_matmul_allgather_multicast(
+        ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.untyped_storage().data_ptr()), out.storage_offset(),
+        strides, ctypes.c_void_p(int(multicast_base)), _DTYPE_CODE[lhs.dtype], dev, ctypes.c_void_p(_stream_ptr(stream)))
     if rc != 0:
         _raise(rc)
     return out

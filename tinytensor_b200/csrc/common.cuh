@@ -85,7 +85,9 @@ struct F32Options {
 };
 // n_peers > 0 fuses an all-gather into the product: every finished tile is also stored into
 // peer_c[i] (peer-mapped pointers to the other GPUs' C, same layout as p.c).
-int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers = 0, void *const *peer_c = nullptr);
+// mc_c: an NVLink multicast address of C (all-gather through the switch); excludes peer_c.
+int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers = 0, void *const *peer_c = nullptr,
+                       void *mc_c = nullptr);
 bool f32_tcgen05_eligible(const Problem &p, char *why, int why_len);
 // two_cta: -1 = pick CTA pairs by shape, 0 = never, 1 = always.
 int launch_i32_tcgen05(const Problem &p, int two_cta = -1, int dbg = 0);

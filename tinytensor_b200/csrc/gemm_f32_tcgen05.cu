@@ -120,6 +120,8 @@ struct alignas(64) TcArgs {
     float *sk_partials;       // stream-K workspace: per unit, CTA and epilogue warp 32 x 128 partial sums
     unsigned int *sk_flags;   // stream-K flags, one per unit, CTA and epilogue warp: 1 while partial sums wait
     int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
+    float *mc_c;   // fused all-gather through an NVLink multicast address of C (same offset and strides
+                   // as `c`): one multimem.st reaches every GPU, this one included; nullptr = off
     int peer_tma;  // 1: the epilogue sends every box to the peers itself with bulk tensor stores
                    // (tmap_peer); 0: the forwarding warps copy finished tiles with st.global
     float *peer_c[kMaxPeers];  // their C, laid out exactly like `c` (same offset and strides)
@@ -369,7 +371,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     const int num_kb = (args.K + BK - 1) / BK;
     const int k_chunk = args.k_chunk > 0 ? args.k_chunk : num_kb;
     // Peers served by the forwarding warps (none when the epilogue's tensor stores reach them).
-    const int fwd_peers = args.peer_tma ? 0 : args.n_peers;
+    const int fwd_peers = (args.peer_tma || args.mc_c != nullptr) ? 0 : args.n_peers;
     const int unit = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
     const int units = PAIR ? (gridDim.x >> 1) : gridDim.x;
     // This unit's segments.  n_store of them store C (all of them with whole tiles); the fused
@@ -816,7 +818,36 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 #pragma unroll
                     for (int j = 0; j < 128; ++j) sum[j] = sum[j] < 0.0f ? 0.0f : sum[j];
                 }
-                if (args.c_tma && fwd_peers == 0) {
+                if (args.mc_c != nullptr && vec_ok) {
+                    // Fused all-gather through the switch: the tile goes once to the multicast
+                    // address of C and NVSwitch delivers it to every GPU (this one included), so
+                    // a GPU sends each byte of its block once, not once per peer.  Same staging
+                    // as below, 8 lanes per row: one instruction stores four 128-byte lines.
+                    uint8_t *stg = tiles + OUT_STAGING_OFFSET + epi_warp * OUT_STAGING_WARP_BYTES;
+                    const int row_base = row - lane;
+                    float *mbase = args.mc_c + static_cast<long long>(b) * args.c_sb;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<float4 *>(stg + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                                make_float4(sum[ch * 32 + 4 * c], sum[ch * 32 + 4 * c + 1], sum[ch * 32 + 4 * c + 2],
+                                            sum[ch * 32 + 4 * c + 3]);
+                        __syncwarp();
+                        const int cc = lane & 7;
+                        const int gcol = col0 + ch * 32 + 4 * cc;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = 4 * i + (lane >> 3);
+                            const float4 v = *reinterpret_cast<const float4 *>(stg + r * 128 + ((cc ^ (r & 7)) << 4));
+                            const int grow = row_base + r;
+                            // the host only takes this path when M is a multiple of 4
+                            if (grow < args.N && gcol < args.M)
+                                multimem_st_v4(mbase + static_cast<long long>(grow) * args.c_si + gcol, v);
+                        }
+                        __syncwarp();
+                    }
+                } else if (args.c_tma && fwd_peers == 0) {
                     // Row-contiguous, 16-byte-aligned C: each warp passes 32 columns at a time
                     // through its 4 KiB of shared memory, written in the 128-byte-swizzled layout
                     // (16-byte chunk XOR row) of a 32 x 32 TMA box, and one lane issues a bulk
@@ -908,7 +939,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         if (lane == 0) {
             bulk_wait_all();
             // stores to peer GPUs must have left this GPU before the kernel is reported complete
-            if (args.n_peers > 0) __threadfence_system();
+            if (args.n_peers > 0 || args.mc_c != nullptr) __threadfence_system();
         }
         if (args.prof && warp == C::FIRST_EPI_WARP && lane == 0) {
             args.prof[blockIdx.x * kProfSlots + kProfEpiAccFull] = w_a;
@@ -1169,17 +1200,26 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     }
     const long long waves = (args.total_tiles + units - 1) / units;
     const double busy = static_cast<double>(args.total_tiles) / static_cast<double>(waves * units);
-    const long long waves_full = args.total_tiles / units, rem = args.total_tiles % units;
+    long long waves_full = args.total_tiles / units;
+    const long long rem = args.total_tiles % units;
     // Whole waves of tiles stay whole; the K blocks of the last partial wave are dealt out over
     // all units (with no whole wave: of every tile).  Each unit needs a few K blocks of that to
     // be worth a fix-up.
+    // Fused all-gather: every tile is cut that way.  Whole waves finish all their tiles at the
+    // same moment, so the exchange would come in bursts with the last one exposed; with every
+    // unit's range crossing tile boundaries at its own time, tiles complete (and leave for the
+    // peers) evenly over the whole kernel.
+    const bool exchange = args.n_peers > 0 || args.mc_c != nullptr;
+    if (exchange && waves_full < 3 && total_kb / units >= 16) waves_full = 0;  // (many waves: the bursts are small)
     const long long cut_tiles = waves_full > 0 ? rem : args.total_tiles;
     const long long cut_kb_per_unit = cut_tiles * num_kb / units;
     const bool sk_worth = waves_full > 0 ? cut_kb_per_unit >= 8
-                                         : ((num_kb >= 64 && cut_kb_per_unit >= 16) || (sk_small && units > args.total_tiles));
+                                         : ((num_kb >= 64 && cut_kb_per_unit >= 16) || (sk_small && units > args.total_tiles) ||
+                                            (exchange && cut_kb_per_unit >= 16));
     const bool sk_possible = cut_tiles > 0 && cut_kb_per_unit >= 4 && cut_tiles * num_kb < 0x7FFFFFFFLL &&
-                             waves_full + 3 <= kMaxSegments;
-    bool streamk = streamk_opt > 0 ? sk_possible : (streamk_opt < 0 && sk_possible && sk_worth && busy < 0.93);
+                             waves_full + 3 <= kMaxSegments && args.total_tiles / units + 3 <= kMaxSegments;
+    bool streamk = streamk_opt > 0 ? sk_possible
+                                   : (streamk_opt < 0 && sk_possible && sk_worth && (busy < 0.93 || exchange));
     args.sk_tile0 = static_cast<int>(waves_full * units);
     if (streamk) {
         int rc = streamk_workspace(p.device, p.stream, &args.sk_partials, &args.sk_flags);
@@ -1201,7 +1241,7 @@ bool f32_tcgen05_eligible(const Problem &p, char *why, int why_len) {
     return plan(p, &pl, why, why_len);
 }
 
-int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, void *const *peer_c) {
+int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, void *const *peer_c, void *mc_c) {
     TcPlan pl;
     char why[200] = "";
     if (!plan(p, &pl, why, sizeof(why))) {
@@ -1252,6 +1292,17 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
     }
     args.n_peers = n_peers;
     for (int i = 0; i < n_peers; ++i) args.peer_c[i] = static_cast<float *>(peer_c[i]);
+    args.mc_c = nullptr;
+    if (mc_c != nullptr) {
+        // multimem.st moves 16 bytes: rows of C must be 16-byte aligned and M a multiple of 4
+        const bool ok = p.c_sj == 1 && (p.c_si & 3) == 0 && (p.c_sb & 3) == 0 && (p.M & 3) == 0 &&
+                        (reinterpret_cast<uintptr_t>(p.c) & 15) == 0 && (reinterpret_cast<uintptr_t>(mc_c) & 15) == 0;
+        if (!ok || n_peers != 0) {
+            set_error("multicast all-gather needs row-contiguous, 16-byte-aligned C with M a multiple of 4 (and no peer list)");
+            return TTB_EUNSUPPORTED;
+        }
+        args.mc_c = static_cast<float *>(mc_c);
+    }
     // When C can be described to TMA here and on every peer, the epilogue sends each box to the
     // peers itself (bulk tensor stores from its staging buffer); otherwise the forwarding warps do.
     args.peer_tma = 0;

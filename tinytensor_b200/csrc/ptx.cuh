@@ -171,6 +171,14 @@ __device__ __forceinline__ void bulk_wait_read_all() {
 }
 // All of this thread's bulk groups are complete (writes performed).
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Store through an NVLink multicast address: the switch delivers the 16 bytes to the same
+// offset of every GPU bound to the multicast object (this one included).
+__device__ __forceinline__ void multimem_st_v4(float *mc_addr, float4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :
+                 : "l"(mc_addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

@@ -564,6 +564,32 @@ TTB_API int ttb_matmul_allgather(const ttb_view *lhs, const ttb_view *rhs, void 
     return launch_f32_tcgen05(p, f32_options(pair), n_peers, peers);
 }
 
+TTB_API int ttb_matmul_allgather_multicast(const ttb_view *lhs, const ttb_view *rhs, void *out, int64_t out_offset,
+                                           const int64_t out_stride[3], void *multicast_out, int dtype, int device_id,
+                                           void *stream) {
+    if (!out_stride || !multicast_out) {
+        set_error("ttb_matmul_allgather_multicast: null out_stride / multicast_out");
+        return TTB_EINVAL;
+    }
+    Problem p{};
+    int rc = resolve(lhs, rhs, out, out_offset, out_stride, dtype, device_id, stream, &p);
+    if (rc != TTB_OK) return rc;
+    char why[160] = "";
+    if (p.dtype != TTB_F32 || !f32_tcgen05_eligible(p, why, sizeof(why))) {
+        set_error("ttb_matmul_allgather_multicast: the fused exchange exists for the f32 tensor-core kernel only (%s)",
+                  p.dtype != TTB_F32 ? "dtype is not f32" : why);
+        return TTB_EUNSUPPORTED;
+    }
+    DeviceState *d;
+    rc = device_state(p.device, &d);
+    if (rc != TTB_OK) return rc;
+    cudaError_t e = cudaSetDevice(p.device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    const long long pair_tiles = ((p.N + 255) / 256) * ((p.M + 255) / 256) * p.B;
+    const bool pair = g_opt.two_cta < 0 ? (p.N > 128 && p.M > 128 && pair_tiles >= 24) : g_opt.two_cta != 0;
+    return launch_f32_tcgen05(p, f32_options(pair), 0, nullptr, static_cast<char *>(multicast_out) + out_offset * 4);
+}
+
 TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, void *out, int dtype,
                                     int device_id) {
     Problem p{};

@@ -64,7 +64,11 @@ class ShardedMatmul:
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None,
                  local_matmul: Optional[Callable[[torch.Tensor, torch.Tensor, torch.Tensor], None]] = None,
-                 col_align: int = COL_ALIGN):
+                 col_align: int = COL_ALIGN, exchange: str = "auto"):
+        # exchange of the fused column-block product: "multicast" = one multimem store per tile
+        # through NVSwitch, "peer" = one store per peer GPU, "auto" = multicast when the
+        # symmetric buffer has a multicast mapping
+        self.exchange = exchange
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -160,9 +164,20 @@ class ShardedMatmul:
         if self._fused_ok(lhs, out):
             # One kernel computes the block and pushes it to every peer; then the ranks meet.
             _, hdl = self._symm
-            peers = [int(hdl.buffer_ptrs[r]) for r in range(self.world) if r != self.rank]
+            block = out[:, :, part.begin:part.end]
+            mc = int(hdl.multicast_ptr) if (self.exchange != "peer" and getattr(hdl, "has_multicast_support", False)) else 0
+            # multimem.st moves 16 bytes: the block's rows must be 16-byte aligned, 4 columns at a time
+            mc_ok = mc != 0 and part.size % 4 == 0 and out.stride(1) % 4 == 0 and out.stride(2) == 1 and \
+                (out.storage_offset() + part.begin) % 4 == 0
+            if self.exchange == "multicast" and not mc_ok:
+                raise backend.TTBError("multicast exchange asked for, but the symmetric buffer has no multicast "
+                                       "mapping or the block is not 16-byte aligned")
             if part.size > 0:
-                backend.matmul_allgather(lhs, rhs[:, :, part.begin:part.end], out[:, :, part.begin:part.end], peers)
+                if mc_ok:
+                    backend.matmul_allgather_multicast(lhs, rhs[:, :, part.begin:part.end], block, mc)
+                else:
+                    peers = [int(hdl.buffer_ptrs[r]) for r in range(self.world) if r != self.rank]
+                    backend.matmul_allgather(lhs, rhs[:, :, part.begin:part.end], block, peers)
             hdl.barrier()
             return out
         parts = [partition(1, N, lhs.shape[2], M, self.world, r, self.col_align) for r in range(self.world)]
