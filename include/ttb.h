@@ -257,6 +257,40 @@ TTB_API int ttb_conv2d_backward(const void *grad_out, const void *input, const v
 TTB_API int ttb_partition(int64_t B, int64_t N, int64_t K, int64_t M, int world, int rank,
                           int64_t col_align, int64_t *begin, int64_t *end);
 
+/* ---- device memory ------------------------------------------------------ */
+
+/* Stream-ordered cached allocation: replaces the cudaMalloc / cudaFree pair of
+ * DeviceMemory<T> (backend/cuda/data_types.cu:38-50, 102-116), each of which
+ * synchronises the whole device.  Blocks come from one CUDA memory pool per
+ * device that never shrinks by itself, so a freed block is handed to the next
+ * request on that stream without a driver call or a synchronisation.  `*ptr`
+ * may be used by work enqueued on `stream` after this call; use on another
+ * stream needs the usual event ordering.  bytes == 0 gives a null pointer and
+ * TTB_OK.  `stream` is a cudaStream_t of `device_id` (NULL = legacy default).
+ * TTB_ENOMEM when the device is out of memory. */
+TTB_API int ttb_device_alloc(void **ptr, uint64_t bytes, int device_id, void *stream);
+/* Returns the block to the pool once the work already enqueued on `stream` has
+ * finished.  NULL is a no-op; a pointer this library did not hand out (or a
+ * second free) is TTB_EINVAL. */
+TTB_API int ttb_device_free(void *ptr, int device_id, void *stream);
+/* Byte counters of ttb_device_alloc on `device_id`, mirroring
+ * StorageCUDA::current_bytes_allocated / total_bytes_allocated
+ * (backend/cuda/storage_cuda.h:66-67): bytes handed out and not yet freed, bytes ever
+ * handed out, and what the pool holds from the driver (live + cached).  Any
+ * out-pointer may be NULL. */
+TTB_API int ttb_device_memory_stats(int device_id, uint64_t *current_bytes, uint64_t *total_bytes,
+                                    uint64_t *reserved_bytes);
+/* Synchronises `device_id` and gives all cached (free) blocks back to the driver. */
+TTB_API int ttb_device_trim(int device_id);
+/* dst[0..bytes) on `dst_device` = src[0..bytes) on `src_device`, enqueued on
+ * `stream` (a stream of dst_device, NULL = legacy default): one peer copy,
+ * direct over NVLink where the devices can map each other (peer access is
+ * switched on at the first copy of a pair), instead of the reference's
+ * device -> host vector -> device bounce of Tensor::to(Device)
+ * (autograd/unary_ops.cpp:67-83).  Same device: a plain device copy. */
+TTB_API int ttb_copy_device_to_device(void *dst, int dst_device, const void *src, int src_device, uint64_t bytes,
+                                      void *stream);
+
 /* ---- introspection / control ------------------------------------------- */
 
 /* Message of the last failing call on this thread ("" if none). */

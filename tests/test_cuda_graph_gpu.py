@@ -1,7 +1,7 @@
 """The products can be recorded into a CUDA graph and replayed (launch-bound loops of small
 products are what graphs are for).  Replays must give the same result as direct calls, also for
-a shape that would use stream-K when launched directly: its ready flags carry a host-chosen
-launch number, so under capture the library records whole-tile work instead."""
+a shape that uses stream-K: its ready flags are raised by the writer and lowered again by the one
+reader, so every launch (and every replay) starts from flags at zero."""
 import numpy as np
 import pytest
 import torch

@@ -138,6 +138,17 @@ def lib() -> ctypes.CDLL:
     L.ttb_device_count.restype = ctypes.c_int
     L.ttb_check_device.argtypes = [ctypes.c_int]
     L.ttb_check_device.restype = ctypes.c_int
+    L.ttb_device_alloc.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_uint64, ctypes.c_int, ctypes.c_void_p]
+    L.ttb_device_alloc.restype = ctypes.c_int
+    L.ttb_device_free.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    L.ttb_device_free.restype = ctypes.c_int
+    L.ttb_device_memory_stats.argtypes = [ctypes.c_int] + [ctypes.POINTER(ctypes.c_uint64)] * 3
+    L.ttb_device_memory_stats.restype = ctypes.c_int
+    L.ttb_device_trim.argtypes = [ctypes.c_int]
+    L.ttb_device_trim.restype = ctypes.c_int
+    L.ttb_copy_device_to_device.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                            ctypes.c_uint64, ctypes.c_void_p]
+    L.ttb_copy_device_to_device.restype = ctypes.c_int
     L.ttb_view_tma_eligible.argtypes = [vp, ctypes.c_int, ctypes.c_int]
     L.ttb_view_tma_eligible.restype = ctypes.c_int
     L.ttb_version.restype = ctypes.c_int
@@ -436,6 +447,62 @@ def batched_matmul_static_scratch(lhs: torch.Tensor, rhs: torch.Tensor, out: tor
     lv, rv = view_of(lhs), view_of(rhs)
     rc = lib().ttb_batched_matmul_static_scratch(ctypes.byref(lv), ctypes.byref(rv), ctypes.c_void_p(out.data_ptr()),
                                                  _DTYPE_CODE[lhs.dtype], dev, ctypes.c_void_p(_stream_ptr(stream)))
+    if rc != 0:
+        _raise(rc)
+    return out
+
+
+def _stream_ptr_on(stream, device: int) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream(int(device))
+    return int(stream.cuda_stream)
+
+
+def device_alloc(nbytes: int, device: int = 0, stream=None) -> int:
+    """Stream-ordered cached allocation (ttb_device_alloc): the address of `nbytes` bytes on `device`,
+    usable by work enqueued on `stream` from now on.  Replaces the cudaMalloc of the reference's
+    DeviceMemory<T> (tinytensor/tensor/backend/cuda/data_types.cu:38-50)."""
+    p = ctypes.c_void_p()
+    rc = lib().ttb_device_alloc(ctypes.byref(p), int(nbytes), int(device), _stream_ptr_on(stream, device))
+    if rc != 0:
+        _raise(rc)
+    return p.value or 0
+
+
+def device_free(ptr: int, device: int = 0, stream=None) -> None:
+    """Give a block of device_alloc back to the pool, in stream order (ttb_device_free; the
+    reference's cudaFree, data_types.cu:102-116)."""
+    rc = lib().ttb_device_free(ctypes.c_void_p(ptr), int(device), _stream_ptr_on(stream, device))
+    if rc != 0:
+        _raise(rc)
+
+
+def device_memory_stats(device: int = 0) -> dict:
+    """Byte counters of device_alloc: `current`, `total` (as StorageCUDA::current_bytes_allocated and
+    total_bytes_allocated, backend/cuda/storage_cuda.h:66) and `reserved` (held by the pool)."""
+    cur, tot, res = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+    rc = lib().ttb_device_memory_stats(int(device), ctypes.byref(cur), ctypes.byref(tot), ctypes.byref(res))
+    if rc != 0:
+        _raise(rc)
+    return {"current": cur.value, "total": tot.value, "reserved": res.value}
+
+
+def device_trim(device: int = 0) -> None:
+    rc = lib().ttb_device_trim(int(device))
+    if rc != 0:
+        _raise(rc)
+
+
+def to_device(t: torch.Tensor, device: int, stream=None) -> torch.Tensor:
+    """Tensor::to(Device) between GPUs as one peer copy (ttb_copy_device_to_device) instead of the
+    reference's bounce through a host vector (tinytensor/autograd/unary_ops.cpp:67-83).  The
+    source is made contiguous first, as to_vec does."""
+    if not t.is_cuda:
+        raise TTBError("to_device: the source must be a CUDA tensor")
+    src = t.contiguous()
+    out = torch.empty(src.shape, dtype=src.dtype, device=f"cuda:{int(device)}")
+    rc = lib().ttb_copy_device_to_device(out.data_ptr(), int(device), src.data_ptr(), src.device.index,
+                                         src.numel() * src.element_size(), _stream_ptr_on(stream, device))
     if rc != 0:
         _raise(rc)
     return out

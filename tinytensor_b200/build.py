@@ -37,6 +37,7 @@ SOURCES = [
     "gemm_f64_dmma.cu",
     "gemm_i32_tcgen05.cu",
     "conv2d.cu",
+    "device_memory.cu",
 ]
 
 

@@ -94,8 +94,9 @@ __global__ void __launch_bounds__(256) im2col_kernel(const U *__restrict__ x, U 
 }
 
 // grad_x[b][c][hi][wi] = sum over (p, q), ascending, of columns[b][c*KK + p*K + q][h*W_out + w]
-// with S*h + p - P == hi and S*w + q - P == wi.  UNIT: stride 1 (no division per tap).
-template <typename T, bool UNIT>
+// with S*h + p - P == hi and S*w + q - P == wi.  UNIT: stride 1 (no division per tap); KT: the
+// kernel size when it is one of the usual ones (3, 5), else 0 and the taps are walked in a loop.
+template <typename T, bool UNIT, int KT>
 __global__ void __launch_bounds__(256) col2im_kernel(const T *__restrict__ cols, T *__restrict__ gx, ConvGeom g,
                                                      long long b0) {
     using A = typename SumOf<T>::type;
@@ -106,6 +107,32 @@ __global__ void __launch_bounds__(256) col2im_kernel(const T *__restrict__ cols,
     const long long bz = blockIdx.z;
     const T *cb = cols + (bz * g.rows + static_cast<long long>(c) * g.K * g.K) * g.pitch;
     A s = A(0);
+    if constexpr (KT > 0) {
+        // Kernel size known at compile time: all K*K loads are issued before the first add (a
+        // thread keeps K*K requests in flight instead of one), then added in (p, q) order.
+        T v[KT > 0 ? KT * KT : 1];
+        bool ok[KT > 0 ? KT * KT : 1];
+#pragma unroll
+        for (int p = 0; p < KT; ++p) {
+            const int hh = hi + g.P - p;
+            const int h = UNIT ? hh : hh / g.S;
+            const bool row_ok = hh >= 0 && (UNIT || hh % g.S == 0) && h < g.H_out;
+#pragma unroll
+            for (int q = 0; q < KT; ++q) {
+                const int ww = wi + g.P - q;
+                const int w = UNIT ? ww : ww / g.S;
+                const bool take = row_ok && ww >= 0 && (UNIT || ww % g.S == 0) && w < g.W_out;
+                ok[p * KT + q] = take;
+                v[p * KT + q] = take ? cb[static_cast<long long>(p * KT + q) * g.pitch + static_cast<long long>(h) * g.W_out + w]
+                                     : T(0);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < KT * KT; ++t)
+            if (ok[t]) s = s + static_cast<A>(v[t]);
+        gx[(((b0 + bz) * g.C_in + c) * g.H_in + hi) * static_cast<long long>(g.W_in) + wi] = static_cast<T>(s);
+        return;
+    }
     for (int p = 0; p < g.K; ++p) {
         const int hh = hi + g.P - p;
         if (hh < 0) break;  // larger p only lowers hh
@@ -196,10 +223,23 @@ template <typename T>
 int typed_col2im(const void *cols, void *gx, const ConvGeom &g, long long b0, long long nb, cudaStream_t st) {
     dim3 grid(static_cast<unsigned>((static_cast<long long>(g.H_in) * g.W_in + 255) / 256),
               static_cast<unsigned>(g.C_in), static_cast<unsigned>(nb));
-    if (g.S == 1)
-        col2im_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T *>(cols), static_cast<T *>(gx), g, b0);
-    else
-        col2im_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T *>(cols), static_cast<T *>(gx), g, b0);
+    const T *src = static_cast<const T *>(cols);
+    T *dst = static_cast<T *>(gx);
+    if (g.S == 1) {
+        if (g.K == 3)
+            col2im_kernel<T, true, 3><<<grid, 256, 0, st>>>(src, dst, g, b0);
+        else if (g.K == 5)
+            col2im_kernel<T, true, 5><<<grid, 256, 0, st>>>(src, dst, g, b0);
+        else
+            col2im_kernel<T, true, 0><<<grid, 256, 0, st>>>(src, dst, g, b0);
+    } else {
+        if (g.K == 3)
+            col2im_kernel<T, false, 3><<<grid, 256, 0, st>>>(src, dst, g, b0);
+        else if (g.K == 5)
+            col2im_kernel<T, false, 5><<<grid, 256, 0, st>>>(src, dst, g, b0);
+        else
+            col2im_kernel<T, false, 0><<<grid, 256, 0, st>>>(src, dst, g, b0);
+    }
     cudaError_t e = cudaGetLastError();
     note_launch(-1, 1);
     return e == cudaSuccess ? TTB_OK : cuda_fail(e, "col2im_kernel launch");

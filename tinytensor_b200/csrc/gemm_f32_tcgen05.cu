@@ -1203,8 +1203,9 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     long long waves_full = args.total_tiles / units;
     const long long rem = args.total_tiles % units;
     // Whole waves of tiles stay whole; the K blocks of the last partial wave are dealt out over
-    // all units (with no whole wave: of every tile).  Each unit needs a few K blocks of that to
-    // be worth a fix-up.
+    // all units (with no whole wave: of every tile).  That replaces a wave of num_kb K blocks
+    // by one of cut_kb_per_unit plus a fix-up (worth a few K blocks), so it pays when the
+    // difference is a dozen K blocks or more.
     // Fused all-gather: every tile is cut that way.  Whole waves finish all their tiles at the
     // same moment, so the exchange would come in bursts with the last one exposed; with every
     // unit's range crossing tile boundaries at its own time, tiles complete (and leave for the
@@ -1213,7 +1214,7 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     if (exchange && waves_full < 3 && total_kb / units >= 16) waves_full = 0;  // (many waves: the bursts are small)
     const long long cut_tiles = waves_full > 0 ? rem : args.total_tiles;
     const long long cut_kb_per_unit = cut_tiles * num_kb / units;
-    const bool sk_worth = waves_full > 0 ? cut_kb_per_unit >= 8
+    const bool sk_worth = waves_full > 0 ? num_kb - cut_kb_per_unit >= 12
                                          : ((num_kb >= 64 && cut_kb_per_unit >= 16) || (sk_small && units > args.total_tiles) ||
                                             (exchange && cut_kb_per_unit >= 16));
     const bool sk_possible = cut_tiles > 0 && cut_kb_per_unit >= 4 && cut_tiles * num_kb < 0x7FFFFFFFLL &&
