@@ -109,6 +109,7 @@ def test_alloc_and_free_inside_a_cuda_graph(ttb):
     a = torch.randn(1, 64, 64, device="cuda")
     out = torch.zeros(1, 64, 64, device="cuda")
     want = ttb.batched_matmul(a, a).clone()
+    L = ttb.lib()
     ttb.device_free(ttb.device_alloc(64 * 64 * 4))  # the pool exists before the capture starts
     torch.cuda.synchronize()
     side = torch.cuda.Stream()
@@ -117,10 +118,13 @@ def test_alloc_and_free_inside_a_cuda_graph(ttb):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
             p = ttb.device_alloc(64 * 64 * 4, stream=side)
-            tmp = _as_tensor(p, 64 * 64).view(1, 64, 64)
-            ttb.batched_matmul(a, a, out=tmp, stream=side)
-            out.copy_(tmp)
-            del tmp
+            # While the capture runs the block is only a reserved address, so it is handed to the
+            # C entry points as a raw pointer (torch cannot wrap it yet).
+            va = ttb.view_of(a)
+            stream = ctypes.c_void_p(side.cuda_stream)
+            assert L.ttb_batched_matmul(ctypes.byref(va), ctypes.byref(va), ctypes.c_void_p(p), 5, 0, stream) == 0
+            assert L.ttb_copy_device_to_device(ctypes.c_void_p(out.data_ptr()), 0, ctypes.c_void_p(p), 0,
+                                               64 * 64 * 4, stream) == 0
             ttb.device_free(p, stream=side)
     torch.cuda.current_stream().wait_stream(side)
     for _ in range(2):
