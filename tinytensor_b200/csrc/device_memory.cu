@@ -215,6 +215,12 @@ TTB_API int ttb_copy_device_to_device(void *dst, int dst_device, const void *src
     }
     e = cudaSetDevice(dst_device);
     if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    if (dst_device == src_device) {
+        // a plain device copy (also what a stream capture accepts)
+        e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync");
+        return TTB_OK;
+    }
     e = cudaMemcpyPeerAsync(dst, dst_device, src, src_device, bytes, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyPeerAsync");
     return TTB_OK;
