@@ -83,11 +83,15 @@ enum { kProfProducerEmpty = 0, kProfMmaAccEmpty, kProfMmaConv, kProfConvSmallEmp
 template <int CG>
 struct Cfg {
     static constexpr int EPI_WGS = CG;                 // one epilogue warpgroup per 128 columns
-    static constexpr int NUM_WARPS = 4 * (2 + EPI_WGS);
+    // Converting a stage is what bounds the kernel.  The one-CTA form gets half the tensor work
+    // out of a converted stage, so it spends its spare warp slots on a second converter
+    // warpgroup (two warps per scheduler hide each other's shared-memory latencies).
+    static constexpr int NUM_CONV_WARPS = CG == 1 ? 8 : 4;
+    static constexpr int NUM_WARPS = 4 + 4 * EPI_WGS + NUM_CONV_WARPS;  // 16 in both forms
     static constexpr int NUM_THREADS = NUM_WARPS * 32;
     static constexpr int FIRST_EPI_WARP = 4;
     static constexpr int FIRST_CONV_WARP = 4 + 4 * EPI_WGS;
-    static constexpr int NUM_CONV_WARPS = 4;
+    static constexpr int EPI_REGS = CG == 1 ? 216 : 184;  // setmaxnreg budget of the epilogue warps
     static constexpr int UMMA_M = BM * CG;
     static constexpr int UMMA_N = BNC * CG;
     static constexpr int ACC_COLS = UMMA_N;            // fp32 columns of one accumulator
@@ -405,12 +409,11 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         }
     };
 
-    // Register budget per warpgroup (CTA-pair form: 512 threads start with 128 registers
-    // each; the epilogue holds 128 accumulators per thread and takes registers the other
-    // roles give up).  Each role's branch starts with its own setmaxnreg so that the
+    // Register budget per warpgroup (512 threads start with 128 registers each; the epilogue
+    // holds 128 accumulators per thread and takes registers the other roles give up).  Each role's branch starts with its own setmaxnreg so that the
     // compiler allocates that branch against its own budget.
     if (warp < C::FIRST_EPI_WARP) {
-      if constexpr (PAIR) setmaxnreg_dec<64>();
+      setmaxnreg_dec<64>();
       if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -653,7 +656,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
       }
     } else if (warp < C::FIRST_CONV_WARP) {
         // ------------------------------------------------------------ epilogue
-        if constexpr (PAIR) setmaxnreg_inc<184>();
+        setmaxnreg_inc<C::EPI_REGS>();
         const int quarter = warp & 3;                         // TMEM lanes [32*quarter, +32)
         const int col_half = (warp - C::FIRST_EPI_WARP) >> 2;  // which 128 accumulator columns
         int acc = 0;
@@ -947,7 +950,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         }
     } else {
         // ------------------------------------------------------------ converters
-        if constexpr (PAIR) setmaxnreg_dec<72>();
+        setmaxnreg_dec<72>();
         const int ctid = threadIdx.x - C::FIRST_CONV_WARP * 32;
         constexpr int NCT = C::NUM_CONV_WARPS * 32;
         int stage = 0;
