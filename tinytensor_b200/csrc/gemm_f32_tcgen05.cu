@@ -32,7 +32,8 @@
 //   epilogue WG  (one per 128 accumulator columns): tcgen05.ld each chunk sum, add into
 //                registers, store C after the last chunk.  Two TMEM accumulators, so the
 //                read-out of chunk i overlaps the MMAs of chunk i+1.
-//   last WG      converters: read the raw tile from shared memory, write the correction
+//   last WG(s)   (one in the pair form, two in the one-CTA form)
+//                converters: read the raw tile from shared memory, write the correction
 //                operands (bf16 tiles in their own swizzled layout, or fp32 `small` tiles at
 //                the same offsets), fence.proxy.async, signal.
 // Two forms: CG = 1, a 128x128 tile per CTA; CG = 2, a 256x256 tile per CTA pair
