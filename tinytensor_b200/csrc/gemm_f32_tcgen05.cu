@@ -179,9 +179,10 @@ __device__ __forceinline__ void report(DeviceStatus *st, volatile int *abort_fla
 // x -> (low part x - trunc_tf32(x), x itself) for the hybrid split's bf16 tiles; both zero
 // for Inf / NaN.
 __device__ __forceinline__ void split_operand(uint32_t bits, float &low, float &whole) {
-    const bool finite = (bits & 0x7F800000u) != 0x7F800000u;
     const float f = __uint_as_float(bits);
-    low = finite ? f - __uint_as_float(bits & 0xFFFFE000u) : 0.0f;
+    const float d = f - __uint_as_float(bits & 0xFFFFE000u);  // Inf - Inf and NaN - NaN give NaN
+    const bool finite = d == d;
+    low = finite ? d : 0.0f;
     whole = finite ? f : 0.0f;
 }
 
@@ -965,6 +966,24 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         if constexpr (PAIR) {
             for (int s = 0; s < SMALL_STAGES; ++s) conv_remote[s] = mapa(smem_u32(&conv_bar[s]), 0);
         }
+        // Hybrid split: where this thread's first 16-byte chunk of a raw operand tile goes in the
+        // bf16 tiles (see the layout note below).  Chunk ctid + u * NCT lands u * NCT * 8 bytes
+        // further in both layouts (NCT chunks are 16 or 32 whole K-major rows, or half a / a whole
+        // MN-major box, and neither changes the XOR terms), so the K loop needs no index math.
+        int hyb_dst0[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const bool mn = half ? (args.b_mn_major != 0) : (args.a_mn_major != 0);
+            const int ci = ctid;
+            if (!mn) {
+                const int r = ci >> 3, cp = ci & 7;
+                hyb_dst0[half] = r * 64 + (cp >> 1) * 16 + (((cp ^ r) & 1) << 3);
+            } else {
+                const int box = ci >> 8, kr = (ci & 255) >> 3, c16 = ci & 7;
+                const int lc = (c16 >> 1) ^ (kr & 3);
+                hyb_dst0[half] = box * 2048 + kr * 64 + ((lc ^ ((kr >> 1) & 3)) << 4) + ((c16 & 1) << 3);
+            }
+        }
         for (int seg = 0; seg < n_seg && ok; ++seg) {
             int t, kb0, kb1;
             segment(seg, t, kb0, kb1);
@@ -999,10 +1018,9 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     //           (k & 3); the bf16 row is 64 B with 16-B chunks XORed by ((k >> 1) & 3).
                     const uint8_t *raw_b = tiles + stage * STAGE_BYTES;
                     uint8_t *out_b = tiles + SMALL_RING_OFFSET + sstage * STAGE_BYTES;
-                    constexpr int PER_T = TILE_BYTES / 16 / NCT;  // 8 chunks per thread per operand tile
+                    constexpr int PER_T = TILE_BYTES / 16 / NCT;  // chunks per thread per operand tile (8 or 4)
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
-                        const bool mn = half ? (args.b_mn_major != 0) : (args.a_mn_major != 0);
                         const uint4 *rt = reinterpret_cast<const uint4 *>(raw_b + half * TILE_BYTES);
                         uint8_t *s16 = out_b + half * 2 * H_TILE_BYTES;
                         uint8_t *x16 = s16 + H_TILE_BYTES;
@@ -1011,16 +1029,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                         for (int u = 0; u < PER_T; ++u) x[u] = rt[ctid + u * NCT];
 #pragma unroll
                         for (int u = 0; u < PER_T; ++u) {
-                            const int ci = ctid + u * NCT;
-                            int dst;
-                            if (!mn) {
-                                const int r = ci >> 3, cp = ci & 7;
-                                dst = r * 64 + (cp >> 1) * 16 + (((cp ^ r) & 1) << 3);
-                            } else {
-                                const int box = ci >> 8, kr = (ci & 255) >> 3, c16 = ci & 7;
-                                const int lc = (c16 >> 1) ^ (kr & 3);
-                                dst = box * 2048 + kr * 64 + ((lc ^ ((kr >> 1) & 3)) << 4) + ((c16 & 1) << 3);
-                            }
+                            const int dst = hyb_dst0[half] + u * (NCT * 8);
                             // Inf and NaN travel through the TF32 product alone: in the bf16 tiles a
                             // non-finite element is replaced by zero, otherwise Inf - Inf would make
                             // its low part NaN and 0 x Inf would turn a correction term into NaN where
