@@ -176,16 +176,6 @@ __device__ __forceinline__ void report(DeviceStatus *st, volatile int *abort_fla
     __threadfence_block();
 }
 
-// x -> (low part x - trunc_tf32(x), x itself) for the hybrid split's bf16 tiles; both zero
-// for Inf / NaN.
-__device__ __forceinline__ void split_operand(uint32_t bits, float &low, float &whole) {
-    const float f = __uint_as_float(bits);
-    const float d = f - __uint_as_float(bits & 0xFFFFE000u);  // Inf - Inf and NaN - NaN give NaN
-    const bool finite = d == d;
-    low = finite ? d : 0.0f;
-    whole = finite ? f : 0.0f;
-}
-
 // Tile order: groups of 8 row tiles sweep all column tiles, so the CTAs running
 // at one time share A rows and B columns in L2.
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &b, int &tm, int &tn) {
@@ -1030,21 +1020,28 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 #pragma unroll
                         for (int u = 0; u < PER_T; ++u) {
                             const int dst = hyb_dst0[half] + u * (NCT * 8);
+                            // low part d = x - trunc_tf32(x) (exact) and x itself, rounded to bf16.
                             // Inf and NaN travel through the TF32 product alone: in the bf16 tiles a
-                            // non-finite element is replaced by zero, otherwise Inf - Inf would make
-                            // its low part NaN and 0 x Inf would turn a correction term into NaN where
-                            // the fp32 result is +-Inf.
-                            float f0, f1, f2, f3, s0, s1, s2, s3;
-                            split_operand(x[u].x, s0, f0);
-                            split_operand(x[u].y, s1, f1);
-                            split_operand(x[u].z, s2, f2);
-                            split_operand(x[u].w, s3, f3);
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(s0, s1), p1 = __floats2bfloat162_rn(s2, s3);
-                            __nv_bfloat162 q0 = __floats2bfloat162_rn(f0, f1), q1 = __floats2bfloat162_rn(f2, f3);
+                            // non-finite element is replaced by zero, otherwise its low part would be
+                            // NaN and 0 x Inf would turn a correction term into NaN where the fp32
+                            // result is +-Inf.  d is NaN exactly for Inf / NaN (Inf - Inf, NaN - NaN),
+                            // so one packed compare of the bf16 pair with itself gives the keep-mask
+                            // of both tiles.
+                            const float f0 = __uint_as_float(x[u].x), f1 = __uint_as_float(x[u].y);
+                            const float f2 = __uint_as_float(x[u].z), f3 = __uint_as_float(x[u].w);
+                            const float d0 = f0 - __uint_as_float(x[u].x & 0xFFFFE000u);
+                            const float d1 = f1 - __uint_as_float(x[u].y & 0xFFFFE000u);
+                            const float d2 = f2 - __uint_as_float(x[u].z & 0xFFFFE000u);
+                            const float d3 = f3 - __uint_as_float(x[u].w & 0xFFFFE000u);
+                            const __nv_bfloat162 p0 = __floats2bfloat162_rn(d0, d1), p1 = __floats2bfloat162_rn(d2, d3);
+                            const __nv_bfloat162 q0 = __floats2bfloat162_rn(f0, f1), q1 = __floats2bfloat162_rn(f2, f3);
+                            const uint32_t m0 = __heq2_mask(p0, p0), m1 = __heq2_mask(p1, p1);
                             *reinterpret_cast<uint2 *>(s16 + dst) =
-                                make_uint2(*reinterpret_cast<uint32_t *>(&p0), *reinterpret_cast<uint32_t *>(&p1));
+                                make_uint2(*reinterpret_cast<const uint32_t *>(&p0) & m0,
+                                           *reinterpret_cast<const uint32_t *>(&p1) & m1);
                             *reinterpret_cast<uint2 *>(x16 + dst) =
-                                make_uint2(*reinterpret_cast<uint32_t *>(&q0), *reinterpret_cast<uint32_t *>(&q1));
+                                make_uint2(*reinterpret_cast<const uint32_t *>(&q0) & m0,
+                                           *reinterpret_cast<const uint32_t *>(&q1) & m1);
                         }
                     }
                 } else if (!(args.dbg & 1))
