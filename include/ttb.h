@@ -287,7 +287,11 @@ TTB_API int ttb_device_trim(int device_id);
  * direct over NVLink where the devices can map each other (peer access is
  * switched on at the first copy of a pair), instead of the reference's
  * device -> host vector -> device bounce of Tensor::to(Device)
- * (autograd/unary_ops.cpp:67-83).  Same device: a plain device copy. */
+ * (autograd/unary_ops.cpp:67-83).  Same device: a plain device copy.
+ * The copy is ordered on `stream` only: work of src_device that produces `src`
+ * on another stream must be ordered before it by the caller (an event).
+ * Like the other device-memory calls it leaves the calling thread's current
+ * device as it found it. */
 TTB_API int ttb_copy_device_to_device(void *dst, int dst_device, const void *src, int src_device, uint64_t bytes,
                                       void *stream);
 

@@ -501,6 +501,11 @@ def to_device(t: torch.Tensor, device: int, stream=None) -> torch.Tensor:
         raise TTBError("to_device: the source must be a CUDA tensor")
     src = t.contiguous()
     out = torch.empty(src.shape, dtype=src.dtype, device=f"cuda:{int(device)}")
+    if src.device.index != int(device) and stream is None:
+        # the copy runs on the destination's stream: order it after the source's pending work
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(src.device))
+        torch.cuda.current_stream(int(device)).wait_event(ready)
     rc = lib().ttb_copy_device_to_device(out.data_ptr(), int(device), src.data_ptr(), src.device.index,
                                          src.numel() * src.element_size(), _stream_ptr_on(stream, device))
     if rc != 0:

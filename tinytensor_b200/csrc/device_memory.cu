@@ -47,6 +47,18 @@ int check_device(int device, const char *who) {
     return TTB_OK;
 }
 
+// These entry points serve any device from any thread: they switch the calling thread to the
+// device they work on and put its previous device back when they return.
+struct DeviceGuard {
+    int prev = -1;
+    DeviceGuard() {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) (void)cudaSetDevice(prev);
+    }
+};
+
 // The device's pool, created on first use.  Caller holds g_mem_mutex.
 int pool_of(int device, PoolState **out) {
     PoolState &ps = g_pools[device];
@@ -93,6 +105,7 @@ TTB_API int ttb_device_alloc(void **ptr, uint64_t bytes, int device_id, void *st
     int rc = check_device(device_id, "ttb_device_alloc");
     if (rc != TTB_OK) return rc;
     if (bytes == 0) return TTB_OK;  // like cudaMalloc(0): success, null pointer
+    DeviceGuard guard;
     std::lock_guard<std::mutex> lock(g_mem_mutex);
     PoolState *ps;
     rc = pool_of(device_id, &ps);
@@ -119,6 +132,7 @@ TTB_API int ttb_device_free(void *ptr, int device_id, void *stream) {
     if (ptr == nullptr) return TTB_OK;
     int rc = check_device(device_id, "ttb_device_free");
     if (rc != TTB_OK) return rc;
+    DeviceGuard guard;
     std::lock_guard<std::mutex> lock(g_mem_mutex);
     PoolState &ps = g_pools[device_id];
     auto it = ps.live.find(ptr);
@@ -158,6 +172,7 @@ TTB_API int ttb_device_memory_stats(int device_id, uint64_t *current_bytes, uint
 TTB_API int ttb_device_trim(int device_id) {
     int rc = check_device(device_id, "ttb_device_trim");
     if (rc != TTB_OK) return rc;
+    DeviceGuard guard;
     std::lock_guard<std::mutex> lock(g_mem_mutex);
     PoolState &ps = g_pools[device_id];
     if (ps.pool == nullptr) return TTB_OK;
@@ -182,6 +197,7 @@ TTB_API int ttb_copy_device_to_device(void *dst, int dst_device, const void *src
     if (rc != TTB_OK) return rc;
     rc = check_device(src_device, "ttb_copy_device_to_device");
     if (rc != TTB_OK) return rc;
+    DeviceGuard guard;
     cudaError_t e;
     if (dst_device != src_device) {
         std::lock_guard<std::mutex> lock(g_mem_mutex);
