@@ -295,6 +295,30 @@ TTB_API int ttb_device_trim(int device_id);
 TTB_API int ttb_copy_device_to_device(void *dst, int dst_device, const void *src, int src_device, uint64_t bytes,
                                       void *stream);
 
+/* ---- seeded inputs (host only) ------------------------------------------
+ *
+ * tinytensor's own random generator, restated so that a benchmark or test
+ * draws exactly the operands a tinytensor program would draw from
+ * Generator(seed) (tinytensor/tensor/random.cpp:17-59: splitmix64 of the seed
+ * gives the state, xorshift64 the outputs).  `*state` is the generator; it
+ * advances by n outputs per distribution call, as the reference's does: a call
+ * on n elements takes n successive outputs, one per element in flat row-major
+ * order, and samples element i from a fresh generator whose state is the i-th
+ * output (backend/cpu/distribution.cpp:31-38, backend/cpu/kernel/distribution.hpp:27-31).
+ * The three distributions are the reference's uniform_real(low, high, shape),
+ * normal(mu, std, shape) and uniform_int(low, high, shape) on its CPU backend
+ * (include/tt/tensor.h:1964-2003, :2204-2210; kernels
+ * backend/common/kernel/distribution.hpp:63-129, :234-245): [low, high) in both
+ * uniform forms.  `out` is HOST memory for n elements of `dtype` (f32 / f64 for
+ * the real-valued ones; i32 / i64 for uniform_int, the reference promotes narrower
+ * integer requests to i32, tensor.cpp:1803-1819).  Values are
+ * bit-identical to the reference library built with the same compiler and libm. */
+TTB_API uint64_t ttb_generator_seed(uint64_t seed);
+TTB_API uint64_t ttb_generator_next(uint64_t *state);
+TTB_API int ttb_generator_uniform_real(uint64_t *state, double low, double high, int64_t n, int dtype, void *out);
+TTB_API int ttb_generator_normal(uint64_t *state, double mu, double sd, int64_t n, int dtype, void *out);
+TTB_API int ttb_generator_uniform_int(uint64_t *state, int64_t low, int64_t high, int64_t n, int dtype, void *out);
+
 /* ---- introspection / control ------------------------------------------- */
 
 /* Message of the last failing call on this thread ("" if none). */

@@ -40,11 +40,12 @@ from .backend import (  # noqa: F401
     tma_eligible,
     view_of,
 )
+from .inputs import CONFIG_SEEDS, Generator, config_operands  # noqa: F401
 from .partition import Partition, ShardedMatmul, partition  # noqa: F401
 
 __all__ = [
     "Activation", "TTBError", "Variant", "batched_matmul", "batched_matmul_fused", "conv2d", "conv2d_backward", "linear", "batched_matmul_host", "batched_matmul_static_scratch",
     "check_device", "device_alloc", "device_free", "device_memory_stats", "device_trim", "to_device", "get_option",
     "last_variant", "launch_count", "lib", "lib_path", "matmul", "matmul_allgather", "matmul_allgather_multicast", "matmul_backward", "set_option", "tma_eligible",
-    "view_of", "Partition", "ShardedMatmul", "partition",
+    "view_of", "Partition", "ShardedMatmul", "partition", "Generator", "config_operands", "CONFIG_SEEDS",
 ]

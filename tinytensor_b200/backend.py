@@ -71,6 +71,13 @@ _NP_DTYPE_CODE = {
 # promote_type_map of the reference (tinytensor/common/scalar.cpp:17-26): the
 # promoted type is the one with the larger enum value.
 _CODE_DTYPE = {v: k for k, v in _DTYPE_CODE.items()}
+# to_string(ScalarType) of the reference (include/tt/scalar.h:76-93), used in its error messages.
+_CODE_NAME = ("bool8", "uint8", "int16", "int32", "int64", "float32", "float64")
+
+
+def _shape_str(t) -> str:
+    """A shape as the reference prints it: (3, 5)."""
+    return "(" + ", ".join(str(int(d)) for d in t.shape) + ")"
 
 _lib = None
 
@@ -518,7 +525,8 @@ def _promote(lhs: torch.Tensor, rhs: torch.Tensor):
         raise TTBError("Unknown ScalarType")
     code = max(_DTYPE_CODE[lhs.dtype], _DTYPE_CODE[rhs.dtype])
     if code == 0:
-        raise TTBError(f"matmul does not support boolean tensors. Given {lhs.dtype} and {rhs.dtype}")
+        raise TTBError("matmul does not support boolean tensors. Given "
+                       f"{_CODE_NAME[_DTYPE_CODE[lhs.dtype]]}, {_CODE_NAME[_DTYPE_CODE[rhs.dtype]]}")
     dt = _CODE_DTYPE[code]
     # A cast yields a contiguous tensor in the reference too (backend/cuda/cast.cu:25-32).
     return (lhs if lhs.dtype == dt else lhs.to(dt)), (rhs if rhs.dtype == dt else rhs.to(dt))
@@ -536,31 +544,35 @@ def matmul(lhs: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
     if ld == 1 and rd == 1:
         if lhs.shape[0] != rhs.shape[0]:
             raise TTBError(f"Invalid shapes for dot product. Both LHS and RHS must have same dimensions: "
-                           f"LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+                           f"LHS={_shape_str(lhs)} and RHS={_shape_str(rhs)}")
         return batched_matmul(lhs.view(1, 1, -1) if lhs.is_contiguous() else lhs.unsqueeze(0).unsqueeze(0),
                               rhs.unsqueeze(0).unsqueeze(2)).flatten()
     if ld == 1 and rd == 2:
         if lhs.shape[0] != rhs.shape[0]:
             raise TTBError(f"Invalid shape for matrix multiplication. Length of LHS should equal size of RHS "
-                           f"dimension 0: LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+                           f"dimension 0: LHS={_shape_str(lhs)} and RHS={_shape_str(rhs)}")
         return batched_matmul(lhs.unsqueeze(0).unsqueeze(0), rhs.unsqueeze(0)).flatten()
     if ld == 2 and rd == 1:
         if lhs.shape[1] != rhs.shape[0]:
             raise TTBError(f"Invalid shape for matrix multiplication. Length of RHS should equal size of LHS "
-                           f"dimension 1: LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+                           f"dimension 1: LHS={_shape_str(lhs)} and RHS={_shape_str(rhs)}")
         return batched_matmul(lhs.unsqueeze(0), rhs.unsqueeze(0).unsqueeze(2)).flatten()
     if ld == 2 and rd == 2:
         if lhs.shape[1] != rhs.shape[0]:
             raise TTBError(f"Invalid shape for matrix multiplication. Size of LHS dimension 1 should equal size "
-                           f"of RHS dimension 0: LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+                           f"of RHS dimension 0: LHS={_shape_str(lhs)} and RHS={_shape_str(rhs)}")
         return batched_matmul(lhs.unsqueeze(0), rhs.unsqueeze(0)).squeeze(0)
     if ld == 3 and rd == 3:
         if lhs.shape[2] != rhs.shape[1]:
             raise TTBError(f"Invalid shape for batched matrix multiplication. Size of LHS dimension 2 should "
-                           f"equal size of RHS dimension 1: LHS={tuple(lhs.shape)} and RHS={tuple(rhs.shape)}")
+                           f"equal size of RHS dimension 1: LHS={_shape_str(lhs)} and RHS={_shape_str(rhs)}")
         return batched_matmul(lhs, rhs)
-    raise TTBError("Unsupported sizes. Try reshaping or broadcasting. Expected dimensions of (LHS=1, RHS=1), "
-                   "(LHS=1, RHS=2), (LHS=2, RHS=1), (LHS=2, RHS=2) or (LHS=3, RHS=3).")
+    raise TTBError("Unsupported sizes. Try reshaping or broadcasting. Expected dimensions of: "
+                   "\n\t(LHS=1, RHS=1) for dot product,"
+                   "\n\t(LHS=1, RHS=2) for vector-matrix product,"
+                   "\n\t(LHS=2, RHS=1) for matrix-vector product,"
+                   "\n\t(LHS=2, RHS=2) for matrix-matrix multiplication, or"
+                   "\n\t(LHS=3, RHS=3) for batched matrix multiplication.")
 
 
 def matmul_backward(lhs: torch.Tensor, rhs: torch.Tensor, grad_output: torch.Tensor):

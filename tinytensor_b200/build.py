@@ -41,6 +41,20 @@ SOURCES = [
 ]
 
 
+# Host-only sources (no device code), compiled by the host compiler: C++20, and the floating-point
+# contraction default of a release build, which the restated input generator must share with the
+# reference library it is pinned against.
+HOST_SOURCES = ["generator.cpp"]
+HOST_FLAGS = ["-std=c++20", "-O3", "-DNDEBUG", "-march=x86-64-v3", "-fPIC", "-fvisibility=hidden", "-pthread"]
+
+
+def _cxx() -> str:
+    exe = os.environ.get("CXX") or shutil.which("g++")
+    if not exe:
+        raise RuntimeError("g++ not found; a C++20 host compiler is required to build libttb.so")
+    return exe
+
+
 def _nvcc() -> str:
     exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(exe):
@@ -55,19 +69,22 @@ def _newest_header() -> float:
 
 def _compile(src: Path, verbose: bool) -> tuple[str, str]:
     obj = OBJ / (src.stem + ".o")
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
+    if src.name in HOST_SOURCES:
+        cmd = [_cxx(), *HOST_FLAGS, "-c", str(src), "-o", str(obj)]
+    else:
+        cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        if verbose:
+            cmd.insert(1, "-Xptxas")
+            cmd.insert(2, "-v")
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
-        raise RuntimeError(f"nvcc failed on {src.name}:\n{r.stdout}\n{r.stderr}")
+        raise RuntimeError(f"compiling {src.name} failed:\n{r.stdout}\n{r.stderr}")
     return src.name, r.stderr
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ.mkdir(exist_ok=True)
-    srcs = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
+    srcs = [CSRC / s for s in SOURCES + HOST_SOURCES if (CSRC / s).exists()]
     hdr_t = _newest_header()
     todo = []
     for s in srcs:
