@@ -8,7 +8,8 @@
 // resolve to ttb_device_alloc / ttb_device_free on the current device and the legacy default
 // stream, the stream every tinytensor kernel runs on (kernel_launch.cuh:24).  The pool caches
 // freed blocks, so a result tensor costs neither cudaMalloc's nor cudaFree's device-wide
-// synchronisation; tinytensor's own byte counters (storage_cuda.h:66-67) are untouched.
+// synchronisation; tinytensor's own byte counters (storage_cuda.h:66-67) are untouched.  Blocks
+// are handed out zero-filled (see pool_malloc).
 //
 // This header is not part of libttb.so.
 #ifndef TTB_TT_ALLOC_SHIM_H_
@@ -41,7 +42,12 @@ inline cudaError_t pool_malloc(void **p, std::size_t bytes) {
         return cudaErrorMemoryAllocation;
     }
     if (trace()) std::fprintf(stderr, "tinytensor DeviceMemory: alloc %p %zu bytes on device %d\n", *p, bytes, device);
-    return cudaSuccess;
+    // tinytensor's pooling backward adds into its freshly allocated grad_input without clearing it
+    // (backend/cuda/conv.cu:526-527, kernel/conv.cuh:216 and :252): that holds only while every
+    // block comes zero-filled from the driver, as new cudaMalloc pages do.  The pool hands back
+    // used blocks, so each one is cleared here, in stream order (a write at HBM speed; still far
+    // cheaper than the cudaMalloc / cudaFree pair it replaces).
+    return bytes ? cudaMemsetAsync(*p, 0, bytes, /*stream=*/nullptr) : cudaSuccess;
 }
 
 inline cudaError_t pool_free(void *p) {
