@@ -146,6 +146,11 @@ TTB_API int ttb_batched_matmul_fused(const ttb_view *lhs, const ttb_view *rhs, v
  * rank, and the ranks have then synchronised with each other (the caller's
  * job: e.g. a symmetric-memory or NCCL barrier on the same stream), every
  * rank holds the complete C.  n_peers == 0 degenerates to the plain product.
+ * Every peer_out[i] must be aligned like `out` modulo 16 bytes (TTB_EINVAL otherwise).
+ * Ordering across ranks is the caller's: besides the barrier AFTER the product, no rank
+ * may start the next product into the same C while another rank still reads the
+ * previous result from its copy (a barrier before the launch, or two C buffers used in
+ * turn -- tinytensor_b200/partition.py does the latter).
  * No counterpart in the reference (single-device matmul, host-bounce copies
  * between devices, autograd/unary_ops.cpp:67-83). */
 TTB_API int ttb_matmul_allgather(const ttb_view *lhs, const ttb_view *rhs, void *out,
@@ -175,7 +180,8 @@ TTB_API int ttb_matmul_allgather_multicast(const ttb_view *lhs, const ttb_view *
  * grown on demand.  Large products are pipelined over three streams so that
  * upload, product and download overlap: a single product (B == 1, rhs rows
  * contiguous) in up to 8 blocks of output columns, a batched one (B >= 4,
- * batch-major operands) in groups of batches.  This is the call a CPU-resident caller makes, the
+ * batch-major operands) in groups of batches.  Calls for one device are serialised
+ * (a second host thread waits until the first call has returned).  This is the call a CPU-resident caller makes, the
  * equivalent of tinytensor's `matmul(a.to(cuda), b.to(cuda)).to(cpu)`
  * (autograd/unary_ops.cpp:67-83 + backend/cuda/matmul.cu:26-78). */
 TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, void *out,
@@ -194,20 +200,24 @@ TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, vo
  * (no cudaMalloc, cudaFree or allocating library routine): it always runs the
  * CUDA-core kernel with K split over thread blocks and keeps the partial sums
  * in a 16 MiB array that is part of the library's device image (every GPU
- * that loads the library holds those 16 MiB until the process exits).
+ * on which the image is loaded holds those 16 MiB until the process exits).
  *
  * Limit: 2 * B * N * M * sizeof(element) must not exceed 16 MiB, otherwise
  * TTB_ELIMIT with a message naming both sizes; nothing is launched then.
  * All dtypes and all strides are accepted; `out` is contiguous [B,N,M].
  *
  * The first call on a device looks up the array's device address
- * (cudaGetSymbolAddress); make that first call before starting any stream
- * capture.  All calls on a device share the one array: two calls whose
- * kernels may overlap on the GPU (different streams, no ordering between
- * them) race on it and give wrong results -- keep calls on one stream or
- * order them with events.  The array keeps whatever the last call left in
- * it; no clearing is needed, because a call overwrites every partial sum it
- * later reads. */
+ * (cudaGetSymbolAddress), which also makes the driver load the library's
+ * device image there -- the moment the 16 MiB are taken from that GPU.  So
+ * make that first call early: before the program hands the remaining device
+ * memory to its own allocator (afterwards the image might not fit), and
+ * before starting any stream capture.  All calls on a device share the one
+ * array: two calls whose kernels may overlap on the GPU (different streams,
+ * no ordering between them) race on it and give wrong results -- keep calls
+ * on one stream or order them with events.  The array keeps whatever the
+ * last call left in it; no clearing is needed, because a call overwrites
+ * every partial sum it later reads.  The calling thread's current device is
+ * left as it was. */
 TTB_API int ttb_batched_matmul_static_scratch(const ttb_view *lhs, const ttb_view *rhs,
                                               void *out, int dtype, int device_id,
                                               void *stream);
@@ -328,6 +338,13 @@ TTB_API int ttb_last_variant(void);
 /* Number of kernels this library has launched on this thread since load. */
 TTB_API int64_t ttb_launch_count(void);
 TTB_API const char *ttb_variant_name(int variant);
+/* Workspaces.  The CUDA-core kernels' K-split partial sums and conv2d's unrolled columns,
+ * weight-gradient partials and padded weights live in cached buffers keyed by
+ * (device, stream), grown with cudaMalloc on demand; calls on different streams never
+ * share one.  A call that would have to grow its buffer while its stream is being
+ * captured into a CUDA graph is refused (TTB_EUNSUPPORTED): make the same call once
+ * before the capture.  Buffers a captured launch has used are never freed. */
+
 /* Options: "force_variant" (enum ttb_variant; AUTO restores dispatch),
  * "tf32_terms" (how the f32 tensor-core kernel reaches fp32-class accuracy:
  * 2 = hybrid split, default: one TF32 product of the operands' high parts plus

@@ -155,3 +155,31 @@ def test_conv2d_and_fused_argument_checks_need_no_gpu(ttb):
     assert fused(None, 5) == -1                                   # unknown activation
     assert fused(None, 1, dtype=3) == -3                          # relu on i32
     assert fused(view((2, 8, 6), (48, 6, -1)), 0) == -1           # negative stride in the addend
+
+
+def test_allgather_peer_arguments_are_checked_on_the_host(ttb):
+    """ttb_matmul_allgather validates its peer pointers before it touches a device: null peers,
+    too many peers, and a peer buffer whose 16-byte alignment differs from this rank's C (the
+    kernel chooses vector or scalar stores from its own C and uses them for every peer)."""
+    from tinytensor_b200.backend import _View
+
+    L = ttb.lib()
+
+    def view(ptr, shape):
+        return _View(ctypes.c_void_p(ptr), 0, (ctypes.c_int64 * 3)(*shape),
+                     (ctypes.c_int64 * 3)(shape[1] * shape[2], shape[2], 1))
+
+    a, b = view(1 << 20, (1, 256, 128)), view(2 << 20, (1, 128, 256))
+    strides = (ctypes.c_int64 * 3)(256 * 256, 256, 1)
+    out = 3 << 20
+
+    def call(peers, n=None):
+        arr = (ctypes.c_void_p * max(len(peers), 1))(*[ctypes.c_void_p(p) for p in peers])
+        return L.ttb_matmul_allgather(ctypes.byref(a), ctypes.byref(b), ctypes.c_void_p(out), 0, strides, arr,
+                                      len(peers) if n is None else n, 5, 0, None)
+
+    assert call([(4 << 20) + 4]) == -1                 # 4-byte aligned peer, 16-byte aligned C: TTB_EINVAL
+    assert b"not aligned like out" in L.ttb_last_error()
+    assert call([0]) == -1                             # null peer
+    assert call([4 << 20] * 16) == -9                  # more than 15 peers: TTB_ELIMIT
+    assert call([4 << 20], n=-1) == -1                 # negative count

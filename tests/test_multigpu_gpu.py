@@ -1,8 +1,11 @@
 """Multi-GPU parity of the partitioner on real devices (skipped with fewer than two GPUs):
 one process per GPU over NCCL.  The column-block product with the all-gather fused into the
 GEMM kernel (three ways to reach the peers, bit-identical to each other) and the NCCL all-gather
-form must agree with each other and with the single-GPU product to a few ulp of max|C|;
-batch-sharded products must equal the unsharded ones."""
+form are checked on EVERY rank against a float64 product (the f32 gate, 1e-5 of max|C|) and
+against each other; back-to-back fused products with changing operands and a read of C between
+them, with no host-side synchronisation, must each be right (the cross-rank ordering rule of
+ShardedMatmul); batch-sharded products (configurations 3 and 5 included) must equal the
+unsharded ones and the oracle; a tensor moved between two GPUs arrives intact."""
 import os
 import socket
 import sys
@@ -45,6 +48,8 @@ def _worker(rank, world, port, q):
             A = torch.randn((1, n, k), generator=g, device=dev)
             B = torch.randn((1, k, m), generator=g, device=dev)
             full = ttb.batched_matmul(A, B)
+            want64 = torch.matmul(A.double(), B.double())
+            gate = lambda x: bool(float((x.double() - want64).abs().max() / want64.abs().max()) <= 1e-5)
             fused = ttb.ShardedMatmul(exchange="peer")
             C = fused.symmetric_output((1, n, m), torch.float32, dev)
             C.fill_(float("nan"))
@@ -53,9 +58,13 @@ def _worker(rank, world, port, q):
             # a shard's K blocks may be dealt out differently from the full product's (stream-K),
             # so sums associate differently: equal to within a few ulp of max|C|, not bit-equal
             close = lambda x: bool(float((x - full).abs().max() / full.abs().max()) <= 2e-6)
-            results[f"{name}_fused"] = close(fused(A, B, out=C))
+            got = fused(A, B, out=C)
+            results[f"{name}_fused"] = close(got)
+            results[f"{name}_fused_vs_float64"] = gate(got)
             plain = ttb.ShardedMatmul()
-            results[f"{name}_nccl"] = close(plain(A, B))
+            got = plain(A, B)
+            results[f"{name}_nccl"] = close(got)
+            results[f"{name}_nccl_vs_float64"] = gate(got)
             # The fused kernel cuts K differently from the plain one (its tiles are made to finish
             # evenly over time, see the kernel), so the two forms agree to rounding, not bit for
             # bit; the three ways the fused kernel can reach the peers deliver the very same sums.
@@ -70,7 +79,7 @@ def _worker(rank, world, port, q):
             ttb.set_option("peer_tma", 1)
             # through NVSwitch multicast (one multimem store per tile), where the symmetric
             # buffer has a multicast mapping
-            if getattr(fused._symm[1], "has_multicast_support", False) and m % (4 * world) == 0:
+            if fused.multicast_available(C) and m % (4 * world) == 0:
                 fused.exchange = "multicast"
                 C.fill_(float("nan"))
                 torch.cuda.synchronize()
@@ -78,6 +87,28 @@ def _worker(rank, world, port, q):
                 results[f"{name}_fused_multicast_eq_tensor_stores"] = bool(torch.equal(fused(A, B, out=C), ref))
                 fused.exchange = "peer"
                 results["multicast_available"] = True
+        # Back-to-back fused products, different operands every time, C read between the calls by
+        # work on the same stream, no host-side synchronisation and no process-group barrier: one
+        # buffer (a barrier goes in front of each rewrite) and two buffers used in turn.
+        n, k, m = 1024, 384, 2048
+        steps = 6
+        As = [torch.randn((1, n, k), generator=g, device=dev) for _ in range(steps)]
+        Bs = [torch.randn((1, k, m), generator=g, device=dev) for _ in range(steps)]
+        wants = [torch.matmul(a.double(), b.double()) for a, b in zip(As, Bs)]
+        for label, nbuf in (("one_buffer", 1), ("two_buffers", 2)):
+            sm = ttb.ShardedMatmul(exchange="peer")
+            bufs = [sm.symmetric_output((1, n, m), torch.float32, dev) for _ in range(nbuf)]
+            errs = torch.zeros(steps, dtype=torch.float64, device=dev)
+            torch.cuda.synchronize()
+            dist.barrier()
+            for i in range(steps):
+                c = sm(As[i], Bs[i], out=bufs[i % nbuf])
+                # the consumer: a full read of this rank's C, enqueued on the same stream
+                errs[i] = (c.double() - wants[i]).abs().max() / wants[i].abs().max()
+                if rank == i % world:
+                    torch.cuda._sleep(2_000_000)   # one rank lags behind: the others must not overwrite what it reads
+            torch.cuda.synchronize()
+            results[f"back_to_back_{label}"] = bool(float(errs.max()) <= 1e-5)
         # column blocks, integer dtype: goes through the NCCL exchange, bit-exact
         Ai = torch.randint(-8, 9, (1, 300, 128), generator=g, device=dev, dtype=torch.int32)
         Bi = torch.randint(-8, 9, (1, 128, 512), generator=g, device=dev, dtype=torch.int32)
@@ -91,6 +122,32 @@ def _worker(rank, world, port, q):
         own = sm(Q, K.permute(0, 2, 1), gather=False)
         results["batch_own"] = bool(torch.equal(own, want[part.begin:part.end]))
         results["batch_gather"] = bool(torch.equal(sm(Q, K.permute(0, 2, 1)), want))
+        # configurations 3 and 5 sharded over the batch dim: seeded operands as the reference draws
+        # them, this rank's share against the oracle (f32 within the gate, i32 bit-exact)
+        sys.path.insert(0, str(ROOT / "tests"))
+        import numpy as np
+        import oracle_lib
+
+        o = oracle_lib.load()
+        p3 = ttb.partition(256, 128, 64, 128, world, rank)
+        ops = ttb.config_operands("c3", batch_range=(p3.begin, p3.end))
+        Qd, Kd, Vd = (torch.from_numpy(ops[k]).to(dev) for k in ("Q", "K", "V"))
+        S = ttb.batched_matmul(Qd, Kd.permute(0, 2, 1))
+        O = ttb.batched_matmul(S, Vd)
+        s64 = np.matmul(ops["Q"].astype(np.float64), ops["K"].astype(np.float64).transpose(0, 2, 1))
+        o64 = np.matmul(S.cpu().numpy().astype(np.float64), ops["V"].astype(np.float64))
+        results["c3_shard_qk"] = bool(np.abs(S.cpu().numpy() - s64).max() / np.abs(s64).max() <= 1e-5)
+        results["c3_shard_sv"] = bool(np.abs(O.cpu().numpy() - o64).max() / np.abs(o64).max() <= 1e-5)
+        p5 = ttb.partition(64, 1024, 512, 1024, world, rank)
+        nb = min(p5.end - p5.begin, 2)   # two batches of the share: the oracle is a CPU loop
+        ops = ttb.config_operands("c5", batch_range=(p5.begin, p5.begin + nb))
+        got = ttb.batched_matmul(torch.from_numpy(ops["A"]).to(dev), torch.from_numpy(ops["B"]).to(dev))
+        results["c5_shard_bit_exact"] = bool(np.array_equal(got.cpu().numpy(), o.matmul(ops["A"], ops["B"])))
+        # Tensor::to(Device) between two GPUs as one peer copy
+        src = torch.randn((3, 1000, 77), generator=g, device=dev)[:, ::2]
+        peer = (rank + 1) % world
+        moved = ttb.to_device(src, peer)
+        results["to_device"] = bool(moved.device.index == peer and torch.equal(moved.cpu(), src.cpu()))
         ttb.check_device(rank)
         torch.cuda.synchronize()
     except Exception as e:  # report instead of hanging the parent

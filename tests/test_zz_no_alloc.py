@@ -94,3 +94,38 @@ def test_static_scratch_refuses_results_beyond_the_fixed_array(ttb):
     assert "scratch" in msg and "16777216" in msg
     with pytest.raises(ttb.TTBError):
         ttb.batched_matmul_static_scratch(a, b, out)
+
+
+def test_static_scratch_calls_leave_device_memory_and_current_device_alone(ttb):
+    """After one warm-up call (which loads the library's device image, scratch array included),
+    further calls of other shapes and dtypes neither take nor return device memory -- seen from
+    the driver (free bytes) and from the library's own pool counters -- and the calling thread's
+    current device stays what it was."""
+    rng = np.random.default_rng(43)
+    cases = []
+    for dt, shape in ((np.float32, (1, 90, 700, 33)), (np.int16, (3, 40, 512, 17)), (np.float64, (1, 16, 2048, 130)),
+                      (np.int64, (2, 33, 300, 65))):
+        B, N, K, M = shape
+        if np.dtype(dt).kind in "iu":
+            a, b = rng.integers(-9, 9, (B, N, K)).astype(dt), rng.integers(-9, 9, (B, K, M)).astype(dt)
+        else:
+            a, b = rng.standard_normal((B, N, K)).astype(dt), rng.standard_normal((B, K, M)).astype(dt)
+        A, Bm = dev(a), dev(b)
+        cases.append((A, Bm, torch.empty((B, N, M), dtype=A.dtype, device="cuda")))
+    assert _call_static(ttb, *cases[0]) == 0, ttb.lib().ttb_last_error()   # warm-up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(0)
+    stats0 = ttb.device_memory_stats(0)
+    device0 = torch.cuda.current_device()
+    for _ in range(2):
+        for A, Bm, out in cases:
+            assert _call_static(ttb, A, Bm, out) == 0, ttb.lib().ttb_last_error()
+            assert torch.cuda.current_device() == device0
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info(0)
+    assert free1 == free0
+    assert ttb.device_memory_stats(0) == stats0
+    for A, Bm, out in cases:
+        assert torch.equal(out, ttb.batched_matmul(A, Bm)) or rel_to_max(
+            host(out), host(ttb.batched_matmul(A, Bm)).astype(np.float64)) <= F32_TOL
+    ttb.check_device(0)

@@ -25,7 +25,7 @@
 
 namespace ttb {
 
-int workspace_slot(int device, int slot, size_t bytes, void **out);
+int workspace_slot(int device, cudaStream_t stream, int slot, size_t bytes, void **out);
 int dispatch_problem(const Problem &p);
 size_t conv_columns_budget();
 
@@ -353,7 +353,7 @@ int weight_rows(const void *weight, const ConvGeom &g, int dtype, int device, cu
     if (dtype != TTB_F32 || (g.rows & 3) == 0) return TTB_OK;
     const long long pitch = (g.rows + 3) / 4 * 4;
     void *buf = nullptr;
-    int rc = workspace_slot(device, 3, static_cast<size_t>(g.C_out) * pitch * 4, &buf);
+    int rc = workspace_slot(device, st, 3, static_cast<size_t>(g.C_out) * pitch * 4, &buf);
     if (rc != TTB_OK) return rc;
     const long long n = static_cast<long long>(g.C_out) * pitch;
     pad_rows_kernel<uint32_t><<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
@@ -387,7 +387,7 @@ extern "C" TTB_API int ttb_conv2d_forward(const void *input, const void *weight,
     const long long B = desc->batch;
     const long long nb_max = chunk_batches(g, B, es);
     void *cols = nullptr;
-    rc = workspace_slot(device_id, 1, static_cast<size_t>(nb_max) * g.rows * g.pitch * es, &cols);
+    rc = workspace_slot(device_id, st, 1, static_cast<size_t>(nb_max) * g.rows * g.pitch * es, &cols);
     if (rc != TTB_OK) return rc;
     const void *w = nullptr;
     long long w_pitch = 0;
@@ -446,12 +446,12 @@ extern "C" TTB_API int ttb_conv2d_backward(const void *grad_out, const void *inp
     const long long B = desc->batch;
     const long long nb_max = chunk_batches(g, B, es);
     void *cols = nullptr, *parts = nullptr;
-    rc = workspace_slot(device_id, 1, static_cast<size_t>(nb_max) * g.rows * g.pitch * es, &cols);
+    rc = workspace_slot(device_id, st, 1, static_cast<size_t>(nb_max) * g.rows * g.pitch * es, &cols);
     if (rc != TTB_OK) return rc;
     const long long wn = static_cast<long long>(g.C_out) * g.rows;
     // also holds the per-item channel sums of grad_bias afterwards
     const long long parts_elems = nb_max * wn > B * g.C_out ? nb_max * wn : B * g.C_out;
-    rc = workspace_slot(device_id, 2, static_cast<size_t>(parts_elems) * es, &parts);
+    rc = workspace_slot(device_id, st, 2, static_cast<size_t>(parts_elems) * es, &parts);
     if (rc != TTB_OK) return rc;
     const void *w = nullptr;
     long long w_pitch = 0;

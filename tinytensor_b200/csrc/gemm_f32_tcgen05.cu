@@ -48,6 +48,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tma_desc.cuh"
@@ -1160,12 +1162,18 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     args.tiles_m = static_cast<int>((p.N + C::TILE_M - 1) / C::TILE_M);
     args.tiles_n = static_cast<int>((p.M + C::TILE_N - 1) / C::TILE_N);
     args.total_tiles = args.tiles_m * args.tiles_n * args.B;
+    // Per-device launch set-up, done once; several host threads may arrive here together.
+    static std::mutex setup_mu;
     static bool attr_set[64] = {false};
+    static int max_clusters[64] = {0};
     auto kernel = gemm_f32_3xtf32_kernel<CG>;
-    if (!attr_set[p.device & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
-        attr_set[p.device & 63] = true;
+    {
+        std::lock_guard<std::mutex> lk(setup_mu);
+        if (!attr_set[p.device & 63]) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
+            attr_set[p.device & 63] = true;
+        }
     }
     cudaLaunchConfig_t cfg{};
     cfg.blockDim = dim3(C::NUM_THREADS);
@@ -1180,7 +1188,7 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        static int max_clusters[64] = {0};
+        std::lock_guard<std::mutex> lk(setup_mu);
         if (max_clusters[p.device & 63] == 0) {
             cfg.gridDim = dim3(static_cast<unsigned>(2 * units));
             int n = 0;
@@ -1234,7 +1242,10 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     args.sk_tile0 = static_cast<int>(waves_full * units);
     if (streamk) {
         int rc = streamk_workspace(p.device, p.stream, &args.sk_partials, &args.sk_flags);
-        if (rc != TTB_OK) streamk = false;  // no workspace for this stream: whole tiles
+        if (rc != TTB_OK) {
+            streamk = false;  // no workspace for this stream: whole tiles, and the call succeeds
+            set_error("%s", "");
+        }
     }
     args.streamk = streamk ? 1 : 0;
     if (!streamk && units > args.total_tiles) units = args.total_tiles;

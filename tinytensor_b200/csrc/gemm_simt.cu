@@ -340,7 +340,7 @@ int launch_tile(const Problem &p, int splits, void *scratch) {
 
 }  // namespace
 
-int workspace_get(int device, size_t bytes, void **out);
+int workspace_get(int device, cudaStream_t stream, size_t bytes, void **out);
 
 namespace {
 
@@ -442,7 +442,7 @@ int launch_skinny_typed(const Problem &p0, int sms) {
         if (splits < 1) splits = 1;
         void *scratch = nullptr;
         if (splits > 1) {
-            int rc = workspace_get(p.device, static_cast<size_t>(splits) * p.B * p.N * p.M * sizeof(T), &scratch);
+            int rc = workspace_get(p.device, p.stream, static_cast<size_t>(splits) * p.B * p.N * p.M * sizeof(T), &scratch);
             if (rc != TTB_OK) return rc;
             a.splits = static_cast<int>(splits);
             a.k_per_split = (p.K + splits - 1) / splits;
@@ -524,7 +524,7 @@ int launch_simt_typed(const Problem &p, bool allow_splitk, bool allow_skinny) {
         if (want >= 2) {
             splits = static_cast<int>(want);
             size_t bytes = static_cast<size_t>(splits) * p.B * p.N * p.M * sizeof(T);
-            int rc = workspace_get(p.device, bytes, &scratch);
+            int rc = workspace_get(p.device, p.stream, bytes, &scratch);
             if (rc != TTB_OK) return rc;
         }
     }
@@ -562,8 +562,9 @@ int launch_simt(const Problem &p, bool allow_splitk, bool allow_skinny) {
 // library would fail or break the budget; and a latency-sensitive loop that cannot accept
 // the device-wide synchronisation cudaMalloc / cudaFree imply.  The ordinary entry points
 // grow a cached workspace with cudaMalloc when the K split needs one; this one never
-// allocates: the partial sums of the K split live in the array below, which every GPU
-// that loads the library holds from load until exit.
+// allocates: the partial sums of the K split live in the array below, which is part of the
+// library's device image: a GPU holds it from the moment that image is loaded there (with the
+// driver's default lazy loading: this entry point's first call on that GPU) until exit.
 namespace ttb {
 namespace {
 
@@ -663,6 +664,16 @@ extern "C" TTB_API int ttb_batched_matmul_static_scratch(const ttb_view *lhs, co
         set_error("device id %d out of range (have %d)", device_id, ndev);
         return TTB_EDEVICE;
     }
+    // This entry point leaves the calling thread's current device as it found it.
+    struct RestoreDevice {
+        int prev = -1;
+        RestoreDevice() {
+            if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        }
+        ~RestoreDevice() {
+            if (prev >= 0) (void)cudaSetDevice(prev);
+        }
+    } restore;
     e = cudaSetDevice(device_id);
     if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
     void *scratch = nullptr;

@@ -14,6 +14,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -49,16 +50,23 @@ struct StreamKSet {
     float *partials;
     unsigned int *flags;
 };
+// A cached scratch buffer.  `captured` records that it was handed to a launch while its stream
+// was being captured: a CUDA graph may then hold the pointer for as long as the process lives.
+struct Workspace {
+    cudaStream_t stream;
+    int slot;
+    void *ptr;
+    size_t bytes;
+    bool captured;
+};
 constexpr int kProfCtas = 256;
 constexpr size_t kProfBytes = kProfCtas * 8 * sizeof(long long);
 struct DeviceState {
     bool init = false;
     int sms = 0;
     DeviceStatus *status = nullptr;
-    void *workspace = nullptr;
-    size_t workspace_bytes = 0;
-    void *extra[kExtraSlots] = {};
-    size_t extra_bytes[kExtraSlots] = {};
+    std::vector<Workspace> ws;   // cached scratch buffers, one per (stream, slot)
+    std::vector<void *> retired; // outgrown buffers a captured graph may still write through
     long long *prof = nullptr;  // kProfCtas x 8 wait-cycle counters of the tcgen05 kernel
     StreamKSet sk[kMaxStreamKSets];
     int sk_count = 0;
@@ -67,6 +75,7 @@ struct DeviceState {
     cudaEvent_t hev[2 * kHostChunks] = {};
     bool hs_init = false;
     size_t stage_bytes[3] = {0, 0, 0};
+    std::mutex host_mu;  // the host-buffer entry point owns the staging buffers and streams for a whole call
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
@@ -194,52 +203,65 @@ int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigne
     return TTB_OK;
 }
 
-// Scratch for split-K partials: cached per device, grown on demand.  Growing
-// frees the old buffer, which synchronises the device, so earlier kernels that
-// used it have finished.
-int workspace_get(int device, size_t bytes, void **out) {
+// Cached scratch buffers, one per (device, stream, slot), grown on demand.  Slot 0: split-K
+// partial sums of the CUDA-core kernels; 1: conv2d's unrolled columns; 2: conv2d's
+// weight-gradient partials; 3: conv2d's padded weights (the products conv2d runs may use slot 0
+// at the same time, hence separate slots).  Keyed by stream so that calls on different streams
+// of one device never share partial sums; calls on ONE stream are ordered by the stream.
+// Growing replaces the buffer: cudaFree synchronises the device, so kernels that still use the
+// old one have finished -- except launches recorded into a CUDA graph, which run again later.
+// Hence a buffer that was handed out during a stream capture is retired (kept allocated) instead
+// of freed, and growing DURING a capture is refused: run the call once before capturing.
+int workspace_slot(int device, cudaStream_t stream, int slot, size_t bytes, void **out) {
     DeviceState *d;
     int rc = device_state(device, &d);
     if (rc != TTB_OK) return rc;
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (d->workspace_bytes < bytes) {
-        if (d->workspace) cudaFree(d->workspace);
-        d->workspace = nullptr;
-        d->workspace_bytes = 0;
-        size_t want = bytes + (bytes >> 2);
-        cudaError_t e = cudaMalloc(&d->workspace, want);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(workspace)");
-        d->workspace_bytes = want;
-    }
-    *out = d->workspace;
-    return TTB_OK;
-}
-
-// Further cached buffers, by slot (1: conv2d columns, 2: conv2d weight-gradient partials,
-// 3: conv2d padded weights).  Slot 0 is the split-K scratch above; the products conv2d runs
-// may use that one at the same time, hence separate slots.
-int workspace_slot(int device, int slot, size_t bytes, void **out) {
-    if (slot == 0) return workspace_get(device, bytes, out);
-    DeviceState *d;
-    int rc = device_state(device, &d);
-    if (rc != TTB_OK) return rc;
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (slot < 1 || slot > kExtraSlots) {
+    if (slot < 0 || slot > kExtraSlots) {
         set_error("workspace slot %d out of range", slot);
         return TTB_EINVAL;
     }
-    void *&buf = d->extra[slot - 1];
-    size_t &have = d->extra_bytes[slot - 1];
-    if (have < bytes) {
-        if (buf) cudaFree(buf);
-        buf = nullptr;
-        have = 0;
-        cudaError_t e = cudaMalloc(&buf, bytes);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(workspace slot)");
-        have = bytes;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaError_t e = cudaStreamIsCapturing(stream, &cap);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamIsCapturing");
+    const bool capturing = cap != cudaStreamCaptureStatusNone;
+    std::lock_guard<std::mutex> lk(g_mu);
+    Workspace *w = nullptr;
+    for (auto &x : d->ws) {
+        if (x.stream == stream && x.slot == slot) w = &x;
     }
-    *out = buf;
+    if (w == nullptr) {
+        d->ws.push_back(Workspace{stream, slot, nullptr, 0, false});
+        w = &d->ws.back();
+    }
+    if (w->bytes < bytes) {
+        if (capturing) {
+            set_error("a %zu-byte workspace is needed but only %zu bytes are cached for this stream: device memory "
+                      "cannot be allocated while the stream is being captured; make the same call once before the capture",
+                      bytes, w->bytes);
+            return TTB_EUNSUPPORTED;
+        }
+        if (w->ptr != nullptr) {
+            if (w->captured) {
+                d->retired.push_back(w->ptr);
+            } else {
+                cudaFree(w->ptr);
+            }
+        }
+        w->ptr = nullptr;
+        w->bytes = 0;
+        w->captured = false;
+        const size_t want = slot == 0 ? bytes + (bytes >> 2) : bytes;
+        e = cudaMalloc(&w->ptr, want);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(workspace)");
+        w->bytes = want;
+    }
+    if (capturing) w->captured = true;
+    *out = w->ptr;
     return TTB_OK;
+}
+
+int workspace_get(int device, cudaStream_t stream, size_t bytes, void **out) {
+    return workspace_slot(device, stream, 0, bytes, out);
 }
 
 static int stage_get(DeviceState *d, int which, size_t bytes, void **out) {
@@ -542,11 +564,7 @@ TTB_API int ttb_matmul_allgather(const ttb_view *lhs, const ttb_view *rhs, void 
                   p.dtype != TTB_F32 ? "dtype is not f32" : why);
         return TTB_EUNSUPPORTED;
     }
-    DeviceState *d;
-    rc = device_state(p.device, &d);
-    if (rc != TTB_OK) return rc;
-    cudaError_t e = cudaSetDevice(p.device);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    // Argument checks first: they need no device.
     void *peers[16];
     if (n_peers > 15) {
         set_error("ttb_matmul_allgather: at most 15 peers, got %d", n_peers);
@@ -558,7 +576,19 @@ TTB_API int ttb_matmul_allgather(const ttb_view *lhs, const ttb_view *rhs, void 
             return TTB_EINVAL;
         }
         peers[i] = static_cast<char *>(peer_out[i]) + out_offset * 4;
+        // The kernel picks vector (16-byte) or scalar stores from THIS GPU's C and then uses the
+        // same kind for every peer: a peer buffer aligned differently would fault in the kernel.
+        if ((reinterpret_cast<uintptr_t>(peers[i]) & 15) != (reinterpret_cast<uintptr_t>(p.c) & 15)) {
+            set_error("ttb_matmul_allgather: peer_out[%d] (%p) is not aligned like out (%p) modulo 16 bytes", i,
+                      peers[i], p.c);
+            return TTB_EINVAL;
+        }
     }
+    DeviceState *d;
+    rc = device_state(p.device, &d);
+    if (rc != TTB_OK) return rc;
+    cudaError_t e = cudaSetDevice(p.device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
     const long long pair_tiles = ((p.N + 255) / 256) * ((p.M + 255) / 256) * p.B;
     const bool pair = g_opt.two_cta < 0 ? (p.N > 128 && p.M > 128 && pair_tiles >= 24) : g_opt.two_cta != 0;
     return launch_f32_tcgen05(p, f32_options(pair), n_peers, peers);
@@ -598,6 +628,9 @@ TTB_API int ttb_batched_matmul_host(const ttb_view *lhs, const ttb_view *rhs, vo
     DeviceState *d;
     rc = device_state(device_id, &d);
     if (rc != TTB_OK) return rc;
+    // One call at a time per device: the staging buffers, the three streams and their events are
+    // shared, so a second host thread waits here until the first call has synchronised.
+    std::lock_guard<std::mutex> host_lock(d->host_mu);
     cudaError_t e = cudaSetDevice(device_id);
     if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
     const size_t es = dtype_size(dtype);

@@ -76,16 +76,26 @@ class ShardedMatmul:
         self._local = local_matmul or (lambda a, b, o: backend.batched_matmul(a, b, out=o))
         self._stage: Optional[torch.Tensor] = None
         self._gathered: Optional[torch.Tensor] = None
-        self._symm = None  # (tensor, symmetric-memory handle) of the fused path's C
+        self._symm = {}          # storage pointer -> (tensor, symmetric-memory handle) of the fused path's C buffers
+        self._last_fused = None  # storage pointer of the C the previous fused product wrote
 
     # -- fused exchange: C lives in symmetric memory so that every rank can store into every C
     def symmetric_output(self, shape, dtype: torch.dtype, device) -> torch.Tensor:
-        """Allocates this rank's C in ``torch.distributed`` symmetric memory and exchanges the
-        peer mappings (a collective: every rank must call it with the same shape).  A product
-        whose `out` is this tensor uses the fused GEMM + all-gather kernel: the column block is
-        computed into it and stored, tile by tile from inside the kernel, into the peers' C
-        over NVLink; one symmetric-memory barrier per product replaces the NCCL all-gather and
-        the re-layout pass."""
+        """Allocates one C buffer of this rank in ``torch.distributed`` symmetric memory and
+        exchanges the peer mappings (a collective: every rank must call it with the same shape).
+        A product whose `out` is such a tensor uses the fused GEMM + all-gather kernel: the column
+        block is computed into it and stored, tile by tile from inside the kernel, into the peers'
+        C over NVLink; one symmetric-memory barrier per product replaces the NCCL all-gather and
+        the re-layout pass.
+
+        Ordering rule.  The kernel of rank s writes into rank r's C.  After the product's barrier
+        every rank holds the complete C and may read it with work enqueued on the same stream.
+        The NEXT product must not start writing into that C while some rank still reads it.  Two
+        ways, both handled by ``__call__``: call this method twice and alternate the two buffers
+        as `out` -- a rank then reaches the product that overwrites a buffer only after every
+        rank has passed the barrier of the product in between, i.e. after all their reads of that
+        buffer, which precede it on their streams; or keep one buffer, and ``__call__`` puts a
+        second barrier in FRONT of every product that writes the buffer the previous one wrote."""
         import torch.distributed._symmetric_memory as symm
 
         t = symm.empty(tuple(shape), dtype=dtype, device=device)
@@ -93,14 +103,20 @@ class ShardedMatmul:
         hdl = symm.rendezvous(t, group.group_name)
         if int(hdl.buffer_ptrs[hdl.rank]) != t.untyped_storage().data_ptr():
             raise backend.TTBError("symmetric buffer does not start at the tensor's storage")
-        self._symm = (t, hdl)
+        self._symm[t.untyped_storage().data_ptr()] = (t, hdl)
         return t
 
-    def _fused_ok(self, lhs: torch.Tensor, out: Optional[torch.Tensor]) -> bool:
-        if self._symm is None or out is None or lhs.dtype != torch.float32:
-            return False
-        t, _ = self._symm
-        return out.untyped_storage().data_ptr() == t.untyped_storage().data_ptr()
+    def multicast_available(self, out: torch.Tensor) -> bool:
+        """True if `out` is a symmetric C buffer of this object with an NVSwitch multicast mapping."""
+        entry = self._symm.get(out.untyped_storage().data_ptr())
+        return bool(entry is not None and getattr(entry[1], "has_multicast_support", False))
+
+    def _fused_handle(self, lhs: torch.Tensor, out: Optional[torch.Tensor]):
+        """The symmetric-memory handle of `out` if the fused exchange applies, else None."""
+        if out is None or lhs.dtype != torch.float32:
+            return None
+        entry = self._symm.get(out.untyped_storage().data_ptr())
+        return entry[1] if entry is not None else None
 
     def plan(self, lhs: torch.Tensor, rhs: torch.Tensor) -> Partition:
         B, N, K = lhs.shape
@@ -161,9 +177,15 @@ class ShardedMatmul:
             if part.size > 0:
                 self._local(lhs, rhs[:, :, part.begin:part.end], out[:, :, part.begin:part.end])
             return out
-        if self._fused_ok(lhs, out):
+        hdl = self._fused_handle(lhs, out)
+        if hdl is not None:
             # One kernel computes the block and pushes it to every peer; then the ranks meet.
-            _, hdl = self._symm
+            key = out.untyped_storage().data_ptr()
+            if self._last_fused == key:
+                # Same C as the product before: every rank must be done reading it before any
+                # rank's kernel stores into it again (see symmetric_output).
+                hdl.barrier()
+            self._last_fused = key
             block = out[:, :, part.begin:part.end]
             mc = int(hdl.multicast_ptr) if (self.exchange != "peer" and getattr(hdl, "has_multicast_support", False)) else 0
             # multimem.st moves 16 bytes: the block's rows must be 16-byte aligned, 4 columns at a time
@@ -176,7 +198,9 @@ class ShardedMatmul:
                 if mc_ok:
                     backend.matmul_allgather_multicast(lhs, rhs[:, :, part.begin:part.end], block, mc)
                 else:
-                    peers = [int(hdl.buffer_ptrs[r]) for r in range(self.world) if r != self.rank]
+                    # peers in ring order starting after this rank, so that at any moment the
+                    # ranks' stores are spread over all receivers instead of converging on one
+                    peers = [int(hdl.buffer_ptrs[(self.rank + i) % self.world]) for i in range(1, self.world)]
                     backend.matmul_allgather(lhs, rhs[:, :, part.begin:part.end], block, peers)
             hdl.barrier()
             return out
