@@ -392,6 +392,11 @@ TTB_API int ttb_tc_profile(int device_id, int64_t *out, int ctas);
  * byte strides multiples of 16), else 0; `operand` 0 = lhs, 1 = rhs.
  * Host-only, touches no device. */
 TTB_API int ttb_view_tma_eligible(const ttb_view *v, int dtype, int operand);
+/* Measures the FP64 tensor-core (DMMA) rate of `device_id` with a register-only loop of the
+ * f64 kernel's own MMA instruction (no memory traffic) and returns it in TFLOP/s: the ceiling
+ * the f64 kernel's roofline fraction is quoted against.  Takes a few milliseconds and
+ * synchronises.  The reference has no such probe (it publishes no performance figures). */
+TTB_API int ttb_measure_fp64_tensor_peak(int device_id, double *tflops);
 TTB_API int ttb_version(void);
 
 #ifdef __cplusplus

@@ -143,6 +143,16 @@ def _worker(rank, world, port, q):
         ops = ttb.config_operands("c5", batch_range=(p5.begin, p5.begin + nb))
         got = ttb.batched_matmul(torch.from_numpy(ops["A"]).to(dev), torch.from_numpy(ops["B"]).to(dev))
         results["c5_shard_bit_exact"] = bool(np.array_equal(got.cpu().numpy(), o.matmul(ops["A"], ops["B"])))
+        # the host-buffer form of the column split: every rank uploads its rows of lhs and its block of rhs
+        hA = torch.randn((1, 1000, 520), generator=torch.Generator().manual_seed(5)).pin_memory()
+        hB = torch.randn((1, 520, 1300), generator=torch.Generator().manual_seed(6)).pin_memory()
+        hC = torch.zeros((1, 1000, 1300)).pin_memory()
+        sm = ttb.ShardedMatmul()
+        sm.columns_from_host(hA, hB, hC)
+        ph = sm.plan(hA, hB)
+        want = torch.matmul(hA.double(), hB.double())[:, :, ph.begin:ph.end]
+        results["columns_from_host"] = bool(ph.size == 0 or float(
+            (hC[:, :, ph.begin:ph.end].double() - want).abs().max() / want.abs().max()) <= 1e-5)
         # Tensor::to(Device) between two GPUs as one peer copy
         src = torch.randn((3, 1000, 77), generator=g, device=dev)[:, ::2]
         peer = (rank + 1) % world

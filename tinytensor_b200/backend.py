@@ -211,6 +211,18 @@ def check_device(device: int = 0) -> None:
         _raise(rc)
 
 
+def measure_fp64_tensor_peak(device: int = 0) -> float:
+    """FP64 tensor-core rate of `device` in TFLOP/s from a register-only loop of the f64 kernel's MMA."""
+    L = lib()
+    L.ttb_measure_fp64_tensor_peak.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+    L.ttb_measure_fp64_tensor_peak.restype = ctypes.c_int
+    out = ctypes.c_double()
+    rc = L.ttb_measure_fp64_tensor_peak(int(device), ctypes.byref(out))
+    if rc != 0:
+        _raise(rc)
+    return out.value
+
+
 def tma_eligible(t: torch.Tensor, operand: int) -> bool:
     v = view_of(t)
     return bool(lib().ttb_view_tma_eligible(ctypes.byref(v), _DTYPE_CODE[t.dtype], operand))

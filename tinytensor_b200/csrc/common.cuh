@@ -93,6 +93,7 @@ bool f32_tcgen05_eligible(const Problem &p, char *why, int why_len);
 int launch_i32_tcgen05(const Problem &p, int two_cta = -1, int dbg = 0);
 bool i32_tcgen05_eligible(const Problem &p, char *why, int why_len);
 int launch_f64_dmma(const Problem &p);
+int measure_fp64_tensor_peak(int device, double *tflops);
 bool f64_dmma_eligible(const Problem &p);
 
 size_t dtype_size(int dtype);

@@ -173,7 +173,64 @@ __global__ void __launch_bounds__(THREADS) gemm_f64_dmma_kernel(DmmaArgs p) {
     }
 }
 
+// The FP64 tensor-core rate itself: every warp keeps the GEMM kernel's 16 independent 16 x 8
+// accumulator tiles in registers and issues m16n8k4 MMAs on register operands, with no memory
+// traffic.  What this loop reaches is the ceiling the GEMM kernel's roofline is quoted against.
+__global__ void __launch_bounds__(THREADS) dmma_peak_kernel(double *sink, int iters, double a_seed, double b_seed) {
+    double acc[MT * NT][4];
+#pragma unroll
+    for (int j = 0; j < MT * NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.0;
+    double a0 = a_seed + threadIdx.x * 1e-9, a1 = a_seed - threadIdx.x * 1e-9, b0 = b_seed;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int j = 0; j < MT * NT; ++j) dmma_m16n8k4(acc[j], a0, a1, b0);
+        b0 = -b0;  // keeps the sums bounded and the loop from being folded
+    }
+    double s = 0.0;
+#pragma unroll
+    for (int j = 0; j < MT * NT; ++j) s += acc[j][0] + acc[j][1] + acc[j][2] + acc[j][3];
+    if (s == 123456.789) sink[0] = s;  // never true: the result only has to look used
+}
+
 }  // namespace
+
+// Runs dmma_peak_kernel on `device` (two CTAs of 8 warps per SM) and returns the best of three
+// launches in TFLOP/s (2 flops per multiply-add of an m16n8k4 MMA).
+int measure_fp64_tensor_peak(int device, double *tflops) {
+    int sms = 0;
+    int rc = sm_count(device, &sms);
+    if (rc != TTB_OK) return rc;
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    double *sink = nullptr;
+    e = cudaMalloc(&sink, sizeof(double));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc");
+    cudaEvent_t t0, t1;
+    cudaEventCreate(&t0);
+    cudaEventCreate(&t1);
+    const int iters = 1 << 14;
+    const int ctas = 2 * sms;
+    const double flop = 2.0 * 16 * 8 * 4 * (MT * NT) * static_cast<double>(iters) * (THREADS / 32) * ctas;
+    double best = 0.0;
+    for (int rep = 0; rep < 4 && e == cudaSuccess; ++rep) {  // the first launch is the warm-up
+        cudaEventRecord(t0, nullptr);
+        dmma_peak_kernel<<<ctas, THREADS>>>(sink, iters, 1.0000001, 0.9999999);
+        cudaEventRecord(t1, nullptr);
+        e = cudaEventSynchronize(t1);
+        float ms = 0.f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, t0, t1);
+        if (e == cudaSuccess && rep > 0 && ms > 0.f && flop / (ms * 1e9) > best) best = flop / (ms * 1e9);
+    }
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+    cudaFree(sink);
+    if (e != cudaSuccess) return cuda_fail(e, "dmma_peak_kernel");
+    note_launch(-1, 4);
+    *tflops = best;
+    return TTB_OK;
+}
 
 bool f64_dmma_eligible(const Problem &p) {
     const long long gy = (p.N + BM - 1) / BM, gz = p.B;

@@ -969,6 +969,14 @@ TTB_API int ttb_tc_profile(int device_id, int64_t *out, int ctas) {
     return TTB_OK;
 }
 
+TTB_API int ttb_measure_fp64_tensor_peak(int device_id, double *tflops) {
+    if (!tflops) {
+        set_error("ttb_measure_fp64_tensor_peak: null output");
+        return TTB_EINVAL;
+    }
+    return measure_fp64_tensor_peak(device_id, tflops);
+}
+
 TTB_API int ttb_view_tma_eligible(const ttb_view *v, int dtype, int operand) {
     if (!v || (operand != 0 && operand != 1)) return 0;
     const size_t es = dtype_size(dtype);

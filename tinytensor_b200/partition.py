@@ -76,6 +76,10 @@ class ShardedMatmul:
         self._local = local_matmul or (lambda a, b, o: backend.batched_matmul(a, b, out=o))
         self._stage: Optional[torch.Tensor] = None
         self._gathered: Optional[torch.Tensor] = None
+        self._host_lhs: Optional[torch.Tensor] = None
+        self._host_rhs: Optional[torch.Tensor] = None
+        self._host_out: Optional[torch.Tensor] = None
+        self._kernel_done: Optional[torch.cuda.Event] = None
         self._symm = {}          # storage pointer -> (tensor, symmetric-memory handle) of the fused path's C buffers
         self._last_fused = None  # storage pointer of the C the previous fused product wrote
 
@@ -134,15 +138,51 @@ class ShardedMatmul:
         return cur[:n].view(*shape)
 
     def __call__(self, lhs: torch.Tensor, rhs: torch.Tensor, out: Optional[torch.Tensor] = None,
-                 gather: bool = True) -> torch.Tensor:
+                 gather: bool = True, kernel_done: Optional[torch.cuda.Event] = None) -> torch.Tensor:
+        """`kernel_done`, if given, is recorded on the current stream right after this rank's
+        product kernel and before any exchange or barrier (for timing breakdowns)."""
         if lhs.dim() != 3 or rhs.dim() != 3:
             raise backend.TTBError("ShardedMatmul expects rank-3 operands")
         B, N, K = lhs.shape
         M = rhs.shape[2]
         part = self.plan(lhs, rhs)
+        self._kernel_done = kernel_done
         if part.kind == "batch":
             return self._batch(lhs, rhs, out, part, gather)
         return self._columns(lhs, rhs, out, part, gather)
+
+    def _mark_kernel_done(self):
+        ev = getattr(self, "_kernel_done", None)
+        if ev is not None:
+            ev.record()
+            self._kernel_done = None
+
+    def columns_from_host(self, lhs_host: torch.Tensor, rhs_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """One column-sharded product whose operands and result live in (pinned) HOST memory, the
+        multi-GPU form of ``batched_matmul_host``: lhs [1,N,K], rhs [1,K,M], out [1,N,M], the same
+        host tensors on every rank.  Rank r uploads only ITS rows of lhs and ITS column block of
+        rhs over its own PCIe link; the rows are all-gathered over NVLink (NCCL) so that every GPU
+        holds lhs; the block product runs; the block of C is downloaded into `out_host`.  Each
+        byte of the operands crosses PCIe once in the whole job, not once per rank.  Synchronises."""
+        _, N, K = lhs_host.shape
+        M = rhs_host.shape[2]
+        part = partition(1, N, K, M, self.world, self.rank, self.col_align)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        rows = (N + self.world - 1) // self.world
+        r0, r1 = min(self.rank * rows, N), min((self.rank + 1) * rows, N)
+        full = self._buffer("_host_lhs", (self.world * rows, K), torch.empty(0, dtype=lhs_host.dtype, device=dev))
+        mine = full[self.rank * rows:self.rank * rows + rows]
+        if r1 > r0:
+            mine[:r1 - r0].copy_(lhs_host[0, r0:r1], non_blocking=True)
+        if self.world > 1:
+            dist.all_gather_into_tensor(full.view(-1), mine.reshape(-1), group=self.group)
+        if part.size > 0:
+            blk = self._buffer("_host_rhs", (1, K, part.size), full)
+            blk.copy_(rhs_host[:, :, part.begin:part.end], non_blocking=True)
+            res = self._buffer("_host_out", (1, N, part.size), full)
+            self._local(full[:N].unsqueeze(0), blk, res)
+            out_host[:, :, part.begin:part.end].copy_(res, non_blocking=True)
+        torch.cuda.synchronize()
 
     # -- batch sharding: no exchange unless the caller wants the full result everywhere
     def _batch(self, lhs, rhs, out, part: Partition, gather: bool):
@@ -152,6 +192,7 @@ class ShardedMatmul:
             out = torch.empty((B, N, M), dtype=lhs.dtype, device=lhs.device)
         if part.size > 0:
             self._local(lhs[part.begin:part.end], rhs[part.begin:part.end], out[part.begin:part.end])
+        self._mark_kernel_done()
         if gather and self.world > 1:
             # Slices are contiguous chunks of [B,N,M]; sizes may differ by one batch.
             chunks = []
@@ -176,6 +217,7 @@ class ShardedMatmul:
         if self.world == 1 or not gather:
             if part.size > 0:
                 self._local(lhs, rhs[:, :, part.begin:part.end], out[:, :, part.begin:part.end])
+            self._mark_kernel_done()
             return out
         hdl = self._fused_handle(lhs, out)
         if hdl is not None:
@@ -202,6 +244,7 @@ class ShardedMatmul:
                     # ranks' stores are spread over all receivers instead of converging on one
                     peers = [int(hdl.buffer_ptrs[(self.rank + i) % self.world]) for i in range(1, self.world)]
                     backend.matmul_allgather(lhs, rhs[:, :, part.begin:part.end], block, peers)
+            self._mark_kernel_done()
             hdl.barrier()
             return out
         parts = [partition(1, N, lhs.shape[2], M, self.world, r, self.col_align) for r in range(self.world)]
@@ -213,6 +256,7 @@ class ShardedMatmul:
         stage = self._buffer("_stage", (1, N, width), lhs)
         if part.size > 0:
             self._local(lhs, rhs[:, :, part.begin:part.end], stage[:, :, :part.size])
+        self._mark_kernel_done()
         gathered = self._buffer("_gathered", (self.world, N, width), lhs)
         dist.all_gather_into_tensor(gathered.view(-1), stage.reshape(-1), group=self.group)
         if equal:
