@@ -392,6 +392,11 @@ TTB_API int ttb_tc_profile(int device_id, int64_t *out, int ctas);
  * byte strides multiples of 16), else 0; `operand` 0 = lhs, 1 = rhs.
  * Host-only, touches no device. */
 TTB_API int ttb_view_tma_eligible(const ttb_view *v, int dtype, int operand);
+/* Tensor maps (TMA descriptors) are built from a view's pointer, extents and strides and kept
+ * in a per-thread cache keyed by exactly those, so a product that comes back with the same
+ * views encodes nothing.  Hits and misses of the calling thread since load; either may be NULL.
+ * The reference has no descriptors (its kernel takes contiguous operands only). */
+TTB_API void ttb_tensor_map_cache_stats(uint64_t *hits, uint64_t *misses);
 /* Measures the FP64 tensor-core (DMMA) rate of `device_id` with a register-only loop of the
  * f64 kernel's own MMA instruction (no memory traffic) and returns it in TFLOP/s: the ceiling
  * the f64 kernel's roofline fraction is quoted against.  Takes a few milliseconds and

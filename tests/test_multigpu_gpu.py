@@ -144,15 +144,16 @@ def _worker(rank, world, port, q):
         got = ttb.batched_matmul(torch.from_numpy(ops["A"]).to(dev), torch.from_numpy(ops["B"]).to(dev))
         results["c5_shard_bit_exact"] = bool(np.array_equal(got.cpu().numpy(), o.matmul(ops["A"], ops["B"])))
         # the host-buffer form of the column split: every rank uploads its rows of lhs and its block of rhs
-        hA = torch.randn((1, 1000, 520), generator=torch.Generator().manual_seed(5)).pin_memory()
-        hB = torch.randn((1, 520, 1300), generator=torch.Generator().manual_seed(6)).pin_memory()
-        hC = torch.zeros((1, 1000, 1300)).pin_memory()
+        fullA = torch.randn((1000, 520), generator=torch.Generator().manual_seed(5))
+        fullB = torch.randn((520, 1300), generator=torch.Generator().manual_seed(6))
         sm = ttb.ShardedMatmul()
-        sm.columns_from_host(hA, hB, hC)
-        ph = sm.plan(hA, hB)
-        want = torch.matmul(hA.double(), hB.double())[:, :, ph.begin:ph.end]
-        results["columns_from_host"] = bool(ph.size == 0 or float(
-            (hC[:, :, ph.begin:ph.end].double() - want).abs().max() / want.abs().max()) <= 1e-5)
+        (r0, r1), (c0, c1) = sm.host_shards(1000, 520, 1300)
+        hA = fullA[r0:r1].contiguous().pin_memory()
+        hB = fullB[:, c0:c1].contiguous().pin_memory()
+        hC = torch.zeros((1000, c1 - c0)).pin_memory()
+        sm.columns_from_host(hA, hB, hC, 1000)
+        want = torch.matmul(fullA.double(), fullB.double())[:, c0:c1]
+        results["columns_from_host"] = bool(c1 == c0 or float((hC.double() - want).abs().max() / want.abs().max()) <= 1e-5)
         # Tensor::to(Device) between two GPUs as one peer copy
         src = torch.randn((3, 1000, 77), generator=g, device=dev)[:, ::2]
         peer = (rank + 1) % world

@@ -12,6 +12,7 @@ compute call raises if ``libttb.so`` is missing.
 """
 from .backend import (  # noqa: F401
     Activation,
+    PreparedMatmul,
     TTBError,
     Variant,
     batched_matmul,
@@ -37,6 +38,7 @@ from .backend import (  # noqa: F401
     matmul_allgather,
     matmul_allgather_multicast,
     measure_fp64_tensor_peak,
+    tensor_map_cache_stats,
     set_option,
     tma_eligible,
     view_of,
@@ -48,5 +50,5 @@ __all__ = [
     "Activation", "TTBError", "Variant", "batched_matmul", "batched_matmul_fused", "conv2d", "conv2d_backward", "linear", "batched_matmul_host", "batched_matmul_static_scratch",
     "check_device", "device_alloc", "device_free", "device_memory_stats", "device_trim", "to_device", "get_option",
     "last_variant", "launch_count", "lib", "lib_path", "matmul", "matmul_allgather", "matmul_allgather_multicast", "matmul_backward", "set_option", "tma_eligible",
-    "view_of", "Partition", "ShardedMatmul", "partition", "Generator", "config_operands", "CONFIG_SEEDS", "measure_fp64_tensor_peak",
+    "view_of", "Partition", "ShardedMatmul", "partition", "Generator", "config_operands", "CONFIG_SEEDS", "measure_fp64_tensor_peak", "PreparedMatmul", "tensor_map_cache_stats",
 ]

@@ -281,6 +281,51 @@ def batched_matmul(lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor | Non
     return out
 
 
+class PreparedMatmul:
+    """``lhs . rhs -> out`` with the C ABI's argument structures built once.
+
+    ``batched_matmul`` checks its tensors and fills two ``ttb_view`` structures on every call,
+    which in Python costs far more than the call itself; a C++ host (the tinytensor-side adapter)
+    fills the same two structures in nanoseconds.  A prepared product is that host's view of the
+    cost: calling it is one foreign call into ``ttb_batched_matmul_strided_out`` with the very
+    same arguments.  The tensors must stay alive and in place; the stream is the one current at
+    preparation unless one is passed to the call."""
+
+    def __init__(self, lhs: torch.Tensor, rhs: torch.Tensor, out: torch.Tensor, stream=None):
+        if lhs.dim() != 3 or rhs.dim() != 3 or out.dim() != 3:
+            raise TTBError("PreparedMatmul expects rank-3 tensors")
+        if not (lhs.device == rhs.device == out.device) or lhs.device.type != "cuda":
+            raise TTBError("PreparedMatmul: operands and result must share a CUDA device")
+        if not (lhs.dtype == rhs.dtype == out.dtype) or lhs.dtype not in _DTYPE_CODE:
+            raise TTBError("PreparedMatmul: operands and result must share a supported dtype")
+        if tuple(out.shape) != (lhs.shape[0], lhs.shape[1], rhs.shape[2]):
+            raise TTBError(f"out has shape {tuple(out.shape)}, expected {(lhs.shape[0], lhs.shape[1], rhs.shape[2])}")
+        self._keep = (lhs, rhs, out)
+        self._lv, self._rv = view_of(lhs), view_of(rhs)
+        self._strides = (ctypes.c_int64 * 3)(*out.stride())
+        dev = lhs.device.index if lhs.device.index is not None else torch.cuda.current_device()
+        self._fn = lib().ttb_batched_matmul_strided_out
+        self._stream = ctypes.c_void_p(_stream_ptr(stream))
+        self._args = (ctypes.byref(self._lv), ctypes.byref(self._rv), ctypes.c_void_p(out.untyped_storage().data_ptr()),
+                      out.storage_offset(), self._strides, _DTYPE_CODE[lhs.dtype], dev)
+
+    def __call__(self, stream=None) -> torch.Tensor:
+        rc = self._fn(*self._args, self._stream if stream is None else ctypes.c_void_p(_stream_ptr(stream)))
+        if rc != 0:
+            _raise(rc)
+        return self._keep[2]
+
+
+def tensor_map_cache_stats():
+    """(hits, misses) of this thread's tensor-map cache (ttb_tensor_map_cache_stats)."""
+    L = lib()
+    L.ttb_tensor_map_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_uint64)] * 2
+    L.ttb_tensor_map_cache_stats.restype = None
+    h, m = ctypes.c_uint64(), ctypes.c_uint64()
+    L.ttb_tensor_map_cache_stats(ctypes.byref(h), ctypes.byref(m))
+    return h.value, m.value
+
+
 class Activation(enum.IntEnum):
     NONE = 0
     RELU = 1

@@ -24,7 +24,53 @@ EncodeFn get_encode_fn() {
     });
     return fn;
 }
+
+// Cache of encoded tensor maps.  A map is a pure function of (first element, extents, strides,
+// element type and size, box, major); products that come back with the same views -- a training
+// loop's weights and activations, a captured sequence replayed call by call -- would otherwise
+// pay three driver encodes per call.  Direct-mapped and per thread: no lock, a collision just
+// re-encodes.  (A freed and re-allocated buffer at the same address with the same shape gives
+// the same map, which is still the right one.)
+struct MapKey {
+    const void *ptr;
+    int64_t mn, k, batch, s_mn, s_k, s_b;
+    int32_t major, dt, es, box_inner, box_mn_rows, box_k_rows;
+    bool operator==(const MapKey &o) const {
+        return ptr == o.ptr && mn == o.mn && k == o.k && batch == o.batch && s_mn == o.s_mn && s_k == o.s_k &&
+               s_b == o.s_b && major == o.major && dt == o.dt && es == o.es && box_inner == o.box_inner &&
+               box_mn_rows == o.box_mn_rows && box_k_rows == o.box_k_rows;
+    }
+};
+struct MapEntry {
+    bool valid = false;
+    MapKey key{};
+    int batch_mul = 0;
+    CUtensorMap map;
+};
+constexpr int kMapCacheSlots = 256;
+thread_local MapEntry g_map_cache[kMapCacheSlots];
+thread_local uint64_t g_map_hits = 0, g_map_misses = 0;
+
+uint32_t map_slot(const MapKey &k) {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+    auto mix = [&](uint64_t v) { h = (h ^ v) * 0xBF58476D1CE4E5B9ull; h ^= h >> 29; };
+    mix(static_cast<uint64_t>(k.mn));
+    mix(static_cast<uint64_t>(k.k));
+    mix(static_cast<uint64_t>(k.batch));
+    mix(static_cast<uint64_t>(k.s_mn));
+    mix(static_cast<uint64_t>(k.s_k));
+    mix(static_cast<uint64_t>(k.s_b));
+    mix((static_cast<uint64_t>(k.major) << 40) ^ (static_cast<uint64_t>(k.dt) << 32) ^ (static_cast<uint64_t>(k.es) << 24) ^
+        (static_cast<uint64_t>(k.box_inner) << 16) ^ (static_cast<uint64_t>(k.box_mn_rows) << 8) ^
+        static_cast<uint64_t>(k.box_k_rows));
+    return static_cast<uint32_t>(h >> 40) % kMapCacheSlots;
+}
 }  // namespace
+
+void tensor_map_cache_stats(uint64_t *hits, uint64_t *misses) {
+    if (hits) *hits = g_map_hits;
+    if (misses) *misses = g_map_misses;
+}
 
 OperandMajor classify_operand(const OperandView &v, size_t es, char *why, int why_len) {
     auto fail = [&](const char *msg) {
@@ -50,6 +96,16 @@ OperandMajor classify_operand(const OperandView &v, size_t es, char *why, int wh
 int encode_operand_tmap(CUtensorMap *map, const OperandView &v, OperandMajor major, CUtensorMapDataType dt,
                         size_t es, int box_inner, int box_mn_rows, int box_k_rows, int *batch_mul, char *why,
                         int why_len) {
+    const MapKey key{v.ptr, v.mn, v.k, v.batch, v.s_mn, v.s_k, v.s_b, static_cast<int32_t>(major),
+                     static_cast<int32_t>(dt), static_cast<int32_t>(es), box_inner, box_mn_rows, box_k_rows};
+    MapEntry &slot = g_map_cache[map_slot(key)];
+    if (slot.valid && slot.key == key) {
+        *map = slot.map;
+        *batch_mul = slot.batch_mul;
+        ++g_map_hits;
+        return 0;
+    }
+    ++g_map_misses;
     EncodeFn fn = get_encode_fn();
     if (!fn) {
         if (why) snprintf(why, why_len, "cuTensorMapEncodeTiled entry point not found");
@@ -100,6 +156,10 @@ int encode_operand_tmap(CUtensorMap *map, const OperandView &v, OperandMajor maj
                      (unsigned long long)gdim[2], (unsigned long long)gstr[0], (unsigned long long)gstr[1]);
         return 1;
     }
+    slot.valid = true;
+    slot.key = key;
+    slot.batch_mul = *batch_mul;
+    slot.map = *map;
     return 0;
 }
 

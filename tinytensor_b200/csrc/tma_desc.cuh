@@ -37,4 +37,8 @@ int encode_operand_tmap(CUtensorMap *map, const OperandView &v, OperandMajor maj
                         size_t elem_size, int box_inner, int box_mn_rows, int box_k_rows, int *batch_mul,
                         char *why, int why_len);
 
+// Hits and misses of the calling thread's tensor-map cache (encode_operand_tmap keeps the maps
+// it has built, keyed by pointer, extents, strides, element type and box).
+void tensor_map_cache_stats(uint64_t *hits, uint64_t *misses);
+
 }  // namespace ttb

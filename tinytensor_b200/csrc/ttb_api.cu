@@ -13,10 +13,12 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <vector>
 
 #include "common.cuh"
+#include "tma_desc.cuh"
 
 namespace ttb {
 
@@ -78,6 +80,7 @@ struct DeviceState {
     std::mutex host_mu;  // the host-buffer entry point owns the staging buffers and streams for a whole call
 };
 DeviceState g_dev[kMaxDevices];
+std::atomic<bool> g_dev_ready[kMaxDevices];  // set once a device's state is initialised: the per-call fast path
 std::mutex g_mu;
 }  // namespace
 
@@ -111,6 +114,10 @@ size_t dtype_size(int dtype) {
 }
 
 static int device_state(int device, DeviceState **out) {
+    if (device >= 0 && device < kMaxDevices && g_dev_ready[device].load(std::memory_order_acquire)) {
+        *out = &g_dev[device];  // every call after the first: no driver query, no lock
+        return TTB_OK;
+    }
     int n = 0;
     cudaError_t e = cudaGetDeviceCount(&n);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceCount");
@@ -135,6 +142,7 @@ static int device_state(int device, DeviceState **out) {
         if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(profile)");
         d.init = true;
     }
+    g_dev_ready[device].store(true, std::memory_order_release);
     *out = &d;
     return TTB_OK;
 }
@@ -968,6 +976,8 @@ TTB_API int ttb_tc_profile(int device_id, int64_t *out, int ctas) {
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(profile)");
     return TTB_OK;
 }
+
+TTB_API void ttb_tensor_map_cache_stats(uint64_t *hits, uint64_t *misses) { tensor_map_cache_stats(hits, misses); }
 
 TTB_API int ttb_measure_fp64_tensor_peak(int device_id, double *tflops) {
     if (!tflops) {

@@ -157,31 +157,41 @@ class ShardedMatmul:
             ev.record()
             self._kernel_done = None
 
-    def columns_from_host(self, lhs_host: torch.Tensor, rhs_host: torch.Tensor, out_host: torch.Tensor) -> None:
-        """One column-sharded product whose operands and result live in (pinned) HOST memory, the
-        multi-GPU form of ``batched_matmul_host``: lhs [1,N,K], rhs [1,K,M], out [1,N,M], the same
-        host tensors on every rank.  Rank r uploads only ITS rows of lhs and ITS column block of
-        rhs over its own PCIe link; the rows are all-gathered over NVLink (NCCL) so that every GPU
-        holds lhs; the block product runs; the block of C is downloaded into `out_host`.  Each
-        byte of the operands crosses PCIe once in the whole job, not once per rank.  Synchronises."""
-        _, N, K = lhs_host.shape
-        M = rhs_host.shape[2]
+    def host_shards(self, N: int, K: int, M: int):
+        """How ``columns_from_host`` splits lhs [N,K] . rhs [K,M] over the ranks: this rank's
+        half-open row range of lhs and column range of rhs / out."""
         part = partition(1, N, K, M, self.world, self.rank, self.col_align)
-        dev = torch.device("cuda", torch.cuda.current_device())
         rows = (N + self.world - 1) // self.world
-        r0, r1 = min(self.rank * rows, N), min((self.rank + 1) * rows, N)
-        full = self._buffer("_host_lhs", (self.world * rows, K), torch.empty(0, dtype=lhs_host.dtype, device=dev))
+        return (min(self.rank * rows, N), min((self.rank + 1) * rows, N)), (part.begin, part.end)
+
+    def columns_from_host(self, lhs_rows_host: torch.Tensor, rhs_block_host: torch.Tensor,
+                          out_block_host: torch.Tensor, N: int) -> None:
+        """One column-sharded product whose operands and result live in (pinned) HOST memory, the
+        multi-GPU form of ``batched_matmul_host`` for one process per GPU, where every process
+        holds a shard of the data: `lhs_rows_host` [rows_r, K] is this rank's row range of lhs,
+        `rhs_block_host` [K, cols_r] its column block of rhs (both as ``host_shards`` cuts them,
+        contiguous), `out_block_host` [N, cols_r] receives its column block of the result.  Each
+        rank uploads only its shards over its own PCIe link; the rows of lhs are all-gathered over
+        NVLink (NCCL) so that every GPU holds all of lhs; the block product runs; the block of C
+        is downloaded.  Each operand byte crosses PCIe once in the whole job, not once per rank.
+        Synchronises."""
+        K = rhs_block_host.shape[0]
+        cols = rhs_block_host.shape[1]
+        dev = torch.device("cuda", torch.cuda.current_device())
+        like = torch.empty(0, dtype=lhs_rows_host.dtype, device=dev)
+        rows = (N + self.world - 1) // self.world
+        full = self._buffer("_host_lhs", (self.world * rows, K), like)
         mine = full[self.rank * rows:self.rank * rows + rows]
-        if r1 > r0:
-            mine[:r1 - r0].copy_(lhs_host[0, r0:r1], non_blocking=True)
+        if lhs_rows_host.shape[0] > 0:
+            mine[:lhs_rows_host.shape[0]].copy_(lhs_rows_host, non_blocking=True)
         if self.world > 1:
             dist.all_gather_into_tensor(full.view(-1), mine.reshape(-1), group=self.group)
-        if part.size > 0:
-            blk = self._buffer("_host_rhs", (1, K, part.size), full)
-            blk.copy_(rhs_host[:, :, part.begin:part.end], non_blocking=True)
-            res = self._buffer("_host_out", (1, N, part.size), full)
+        if cols > 0:
+            blk = self._buffer("_host_rhs", (1, K, cols), like)
+            blk[0].copy_(rhs_block_host, non_blocking=True)
+            res = self._buffer("_host_out", (1, N, cols), like)
             self._local(full[:N].unsqueeze(0), blk, res)
-            out_host[:, :, part.begin:part.end].copy_(res, non_blocking=True)
+            out_block_host.copy_(res[0], non_blocking=True)
         torch.cuda.synchronize()
 
     # -- batch sharding: no exchange unless the caller wants the full result everywhere
