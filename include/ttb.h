@@ -366,6 +366,11 @@ TTB_API const char *ttb_variant_name(int variant);
  * "peer_tma" (1, default: ttb_matmul_allgather reaches the peers with bulk
  * tensor stores issued by the epilogue; 0: dedicated warps copy finished tiles
  * with st.global),
+ * "a_tmem" (0, default; 1: the f32 kernel's correction products read their A operands from
+ * tensor memory, where the converters put them, instead of shared memory -- measured: no
+ * faster, the pair form then has room for one accumulator only),
+ * "extra_conv" (1, default: the two spare warps of the f32 pair kernel convert half of every
+ * rhs tile; 0: converter warpgroup only),
  * "tc_debug" (bit mask of timing / fault-handling experiments of the f32
  * tensor-core kernel, test only: results are wrong or absent when set).
  * Returns TTB_EINVAL for an unknown key or value. */

@@ -285,3 +285,29 @@ def test_denormal_operands(forced):
     bound = 2.0 ** -136 * np.abs(b).astype(np.float64).sum(axis=1).max()  # 2^-136 |b| per term, worst column
     assert np.abs(got - want).max() <= bound
     assert rel_to_max(got, want) <= 5e-2
+
+
+@pytest.mark.parametrize("option,value", [("a_tmem", 1), ("extra_conv", 0)])
+@pytest.mark.parametrize("shape", [(2, 256, 512, 256), (1, 379, 1147, 635), (8, 128, 64, 128)])
+def test_converter_variants_meet_f32_tolerance_all_layouts(forced, shape, option, value):
+    """Two switches of the hybrid split's converters, all four operand majors, both kernel forms:
+    `a_tmem` = 1 puts the A operands of the correction products into tensor memory (written by the
+    converters with tcgen05.st, read by the MMAs in their A-from-TMEM form; the pair form then
+    keeps one accumulator); `extra_conv` = 0 takes the two spare warps of the pair form out of the
+    conversion (the default has them convert half of every B tile)."""
+    rng = np.random.default_rng(77)
+    B, N, K, M = shape
+    a = dev(rng.standard_normal((B, N, K)).astype(np.float32))
+    b = dev(rng.standard_normal((B, K, M)).astype(np.float32))
+    want = np.matmul(host(a).astype(np.float64), host(b).astype(np.float64))
+    forced.set_option(option, value)
+    try:
+        for name, (av, bv) in layouts(a, b).items():
+            if forced.get_option("force_variant") == int(forced.Variant.TCGEN05_2CTA) and (N <= 128 or M <= 128):
+                continue
+            got = forced.batched_matmul(av, bv)
+            assert rel_to_max(host(got), want) <= F32_TOL, (name, option)
+        forced.check_device(0)
+    finally:
+        forced.set_option("a_tmem", 0)
+        forced.set_option("extra_conv", 1)

@@ -82,6 +82,8 @@ struct F32Options {
     int dbg = 0;        // timing experiments (wrong results when non-zero)
     int streamk = -1;   // K blocks dealt out evenly over the SMs: -1 automatic, 0 never, 1 whenever possible
     int peer_tma = 1;   // fused all-gather: peers are reached by the epilogue's bulk tensor stores when possible
+    int a_tmem = 0;     // hybrid split: A operands of the correction MMAs in tensor memory
+    int extra_conv = 1; // pair form: the two spare warps of the producer warpgroup convert too
 };
 // n_peers > 0 fuses an all-gather into the product: every finished tile is also stored into
 // peer_c[i] (peer-mapped pointers to the other GPUs' C, same layout as p.c).

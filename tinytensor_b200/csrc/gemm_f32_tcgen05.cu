@@ -98,7 +98,13 @@ struct Cfg {
     static constexpr int UMMA_M = BM * CG;
     static constexpr int UMMA_N = BNC * CG;
     static constexpr int ACC_COLS = UMMA_N;            // fp32 columns of one accumulator
-    static constexpr int TMEM_COLS = 2 * ACC_COLS;     // two accumulators
+    static constexpr int TMEM_COLS = 512;              // accumulators + the A operands of the correction MMAs
+    // Tensor memory map (512 columns).  A operands of the hybrid split's correction products
+    // (args.a_tmem): SMALL_STAGES slots of 32 columns -- 16 columns bf16(small A), 16 columns
+    // bf16(A), two K elements per column -- behind the accumulators.  The pair form's
+    // accumulator is 256 columns wide, so with the A slots there is room for ONE (the epilogue
+    // drains it between chunks); without them, and in the one-CTA form, there are two.
+    static constexpr int A_SLOT_COLS = 32;
     static constexpr int TILE_M = BM * CG;             // rows of C per CTA (pair)
     static constexpr int TILE_N = BNC * CG;
 };
@@ -119,6 +125,9 @@ struct alignas(64) TcArgs {
     int a_mn_major, b_mn_major;
     int a_batch_mul, b_batch_mul;
     int tiles_m, tiles_n, total_tiles;
+    int a_tmem;    // hybrid split: the correction MMAs read their A operands from tensor memory
+    int extra_conv;  // pair form, hybrid split: warps 2-3 convert too (set by the host when they have no
+                     // forwarding to do)
     int terms;     // 3 = split-TF32, 1 = single pass (test only)
     int k_chunk;   // K blocks per TMEM accumulation chunk
     int mask_big;  // converters also overwrite the raw tile with its masked big part
@@ -163,6 +172,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
             if (waited) *waited += clock64() - c0;
             return true;
         }
+
         if ((i & 63u) == 63u) {
             if (*abort_flag) return false;
             const unsigned long long now = global_ns();
@@ -176,6 +186,46 @@ __device__ __forceinline__ void report(DeviceStatus *st, volatile int *abort_fla
     if (atomicCAS(&st->error, 0u, code) == 0u) st->detail = detail;
     *abort_flag = 1;
     __threadfence_block();
+}
+
+// Hybrid split of one 16-byte chunk of a raw operand tile (4 fp32): low part d = x - trunc_tf32(x)
+// (exact) and x itself, both rounded to bf16, 8 bytes each, at offset `dst` of the two bf16 tiles.
+// Inf and NaN travel through the TF32 product alone: in the bf16 tiles a non-finite element is
+// replaced by zero, otherwise its low part would be NaN and 0 x Inf would turn a correction term
+// into NaN where the fp32 result is +-Inf.  d is NaN exactly for Inf / NaN (Inf - Inf, NaN - NaN),
+// so one packed compare of the bf16 pair with itself gives the keep-mask of both tiles.
+__device__ __forceinline__ void hybrid_chunk(const uint4 x, uint8_t *s16, uint8_t *x16, int dst) {
+    const float f0 = __uint_as_float(x.x), f1 = __uint_as_float(x.y);
+    const float f2 = __uint_as_float(x.z), f3 = __uint_as_float(x.w);
+    const float d0 = f0 - __uint_as_float(x.x & 0xFFFFE000u);
+    const float d1 = f1 - __uint_as_float(x.y & 0xFFFFE000u);
+    const float d2 = f2 - __uint_as_float(x.z & 0xFFFFE000u);
+    const float d3 = f3 - __uint_as_float(x.w & 0xFFFFE000u);
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(d0, d1), p1 = __floats2bfloat162_rn(d2, d3);
+    const __nv_bfloat162 q0 = __floats2bfloat162_rn(f0, f1), q1 = __floats2bfloat162_rn(f2, f3);
+    const uint32_t m0 = __heq2_mask(p0, p0), m1 = __heq2_mask(p1, p1);
+    *reinterpret_cast<uint2 *>(s16 + dst) = make_uint2(*reinterpret_cast<const uint32_t *>(&p0) & m0,
+                                                       *reinterpret_cast<const uint32_t *>(&p1) & m1);
+    *reinterpret_cast<uint2 *>(x16 + dst) = make_uint2(*reinterpret_cast<const uint32_t *>(&q0) & m0,
+                                                       *reinterpret_cast<const uint32_t *>(&q1) & m1);
+}
+
+// Where the 16-byte chunk `ci` of a raw operand tile goes in the bf16 tiles, from undoing the raw
+// tile's swizzle:
+//  K-major  raw rows are 128 B with 16-B chunks XORed by (row & 7); the bf16 row is 64 B with
+//           16-B chunks XORed by ((row >> 1) & 3) -- the XORs cancel up to the low bit, which
+//           picks the half of the 16-byte chunk.
+//  MN-major raw rows (one K index, 32 MN values) have 32-B chunks XORed by (k & 3); the bf16 row
+//           is 64 B with 16-B chunks XORed by ((k >> 1) & 3).
+// Chunks 8 rows (64 chunks) apart land 512 bytes apart in both layouts.
+__device__ __forceinline__ int hybrid_dst(int ci, bool mn_major) {
+    if (!mn_major) {
+        const int r = ci >> 3, cp = ci & 7;
+        return r * 64 + (cp >> 1) * 16 + (((cp ^ r) & 1) << 3);
+    }
+    const int box = ci >> 8, kr = (ci & 255) >> 3, c16 = ci & 7;
+    const int lc = (c16 >> 1) ^ (kr & 3);
+    return box * 2048 + kr * 64 + ((lc ^ ((kr >> 1) & 3)) << 4) + ((c16 & 1) << 3);
 }
 
 // Tile order: groups of 8 row tiles sweep all column tiles, so the CTAs running
@@ -308,7 +358,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             mbar_init(&empty_bar[s], 1);
         }
         for (int s = 0; s < SMALL_STAGES; ++s) {
-            mbar_init(&conv_bar[s], C::NUM_CONV_WARPS * CG);
+            // converter warps of both CTAs, plus the two extra ones per CTA of the pair form (below)
+            mbar_init(&conv_bar[s], (C::NUM_CONV_WARPS + ((PAIR && args.terms == 2 && args.extra_conv) ? 2 : 0)) * CG);
             mbar_init(&small_empty_bar[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -365,6 +416,14 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
+    // A operands in tensor memory (hybrid split only): see the map at Cfg.
+    const bool a_tmem = args.a_tmem != 0 && args.terms == 2 && !(args.dbg & 8);
+    const int acc_bufs = (a_tmem && PAIR) ? 1 : 2;
+    // The pair form has one converter warp per scheduler, and converting is what bounds the kernel;
+    // its warps 2-3 have nothing to do unless they forward tiles to peers (the fallback form of the
+    // fused all-gather), so they convert the second half of every B tile.
+    const bool extra_conv = PAIR && args.terms == 2 && args.extra_conv != 0;
+    const uint32_t a_slot_col0 = static_cast<uint32_t>(acc_bufs * C::ACC_COLS);
 
     const int num_kb = (args.K + BK - 1) / BK;
     const int k_chunk = args.k_chunk > 0 ? args.k_chunk : num_kb;
@@ -505,6 +564,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             //  MN-major: 32-element MN groups 2048 B apart (LBO), 8-row K groups 512 B apart
             //            (SBO); a K step of 16 rows advances by 1024 B.
             const uint32_t idesc16 = make_idesc_bf16(C::UMMA_M, C::UMMA_N, args.a_mn_major, args.b_mn_major);
+            // A read from tensor memory is K-major whatever the raw tile's layout was
+            const uint32_t idesc16_ts = make_idesc_bf16(C::UMMA_M, C::UMMA_N, 0, args.b_mn_major);
             const uint32_t a16_lbo = args.a_mn_major ? 2048 : 16, a16_kstep = args.a_mn_major ? 1024 : 32;
             const uint32_t b16_lbo = args.b_mn_major ? 2048 : 16, b16_kstep = args.b_mn_major ? 1024 : 32;
             uint32_t peer_empty[STAGES], peer_small_empty[SMALL_STAGES], peer_acc_full[2];
@@ -549,7 +610,19 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                             }
                             const uint32_t a_s16 = a_small, a_x16 = a_small + H_TILE_BYTES;
                             const uint32_t b_s16 = a_small + 2 * H_TILE_BYTES, b_x16 = a_small + 3 * H_TILE_BYTES;
-                            if (!(args.dbg & 8)) {
+                            if (a_tmem) {
+                                // A operands of the corrections from tensor memory (the converters put
+                                // them there): no shared-memory read for them, and none was written.
+                                const uint32_t t_s = tmem_base + a_slot_col0 + static_cast<uint32_t>(sstage * C::A_SLOT_COLS);
+                                const uint32_t t_x = t_s + 16;
+#pragma unroll
+                                for (int k2 = 0; k2 < BK / 16; ++k2) {
+                                    mma_f16_ts<CG>(d_tmem, t_s + k2 * 8,
+                                                   make_smem_desc(b_x16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16_ts, 1);
+                                    mma_f16_ts<CG>(d_tmem, t_x + k2 * 8,
+                                                   make_smem_desc(b_s16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16_ts, 1);
+                                }
+                            } else if (!(args.dbg & 8)) {
 #pragma unroll
                                 for (int k2 = 0; k2 < BK / 16; ++k2) {
                                     mma_f16<CG>(d_tmem, make_smem_desc(a_s16 + k2 * a16_kstep, a16_lbo, 512, kSwizzle64),
@@ -599,8 +672,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     if (!ok) break;
                     mma_commit<CG>(smem_u32(&acc_full_bar[acc]));
                     if constexpr (PAIR) mma_commit<CG>(peer_acc_full[acc]);
-                    acc ^= 1;
-                    if (acc == 0) acc_phase ^= 1u;
+                    if (++acc == acc_bufs) {
+                        acc = 0;
+                        acc_phase ^= 1u;
+                    }
                 }
             }
             // Everything issued must have retired before TMEM is freed.
@@ -647,6 +722,51 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         }
         // Peer stores must have left this GPU before the kernel is reported complete.
         __threadfence_system();
+      } else if (extra_conv) {
+        // ------------------------------------------------------------ extra converters (warps 2-3, pair form)
+        // Chunks [512, 1024) of every raw B tile: thread e takes 512 + e + 64 u, u = 0..7, which
+        // land 512 bytes apart in the bf16 tiles (see hybrid_dst).  Same waits and the same
+        // converted barrier as the converter warpgroup.
+        const int etid = threadIdx.x - 64;  // 0..63
+        const int dst0 = hybrid_dst(512 + etid, args.b_mn_major != 0);
+        const uint32_t conv_remote0 = PAIR ? mapa(smem_u32(&conv_bar[0]), 0) : 0u;
+        int stage = 0, sstage = 0;
+        uint32_t phase = 0, sphase = 0;
+        bool ok = true;
+        for (int seg = 0; seg < n_seg && ok; ++seg) {
+            int t, kb0, kb1;
+            segment(seg, t, kb0, kb1);
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!wait_or_abort<PAIR>(&small_empty_bar[sstage], sphase ^ 1u, abort_flag) ||
+                    !wait_or_abort<false>(&full_bar[stage], phase, abort_flag)) {
+                    if (lane == 0) report(args.status, abort_flag, kErrConverterWait, 64u + static_cast<unsigned>(stage));
+                    ok = false;
+                    break;
+                }
+                const uint4 *rt = reinterpret_cast<const uint4 *>(tiles + stage * STAGE_BYTES + TILE_BYTES) + 512 + etid;
+                uint8_t *s16 = tiles + SMALL_RING_OFFSET + sstage * STAGE_BYTES + 2 * H_TILE_BYTES;
+                uint8_t *x16 = s16 + H_TILE_BYTES;
+#pragma unroll
+                for (int b4 = 0; b4 < 8; b4 += 4) {
+                    uint4 x[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) x[u] = rt[(b4 + u) * 64];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) hybrid_chunk(x[u], s16, x16, dst0 + (b4 + u) * 512);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(conv_remote0 + static_cast<uint32_t>(sstage * sizeof(uint64_t)));
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+                if (++sstage == SMALL_STAGES) {
+                    sstage = 0;
+                    sphase ^= 1u;
+                }
+            }
+        }
       }
     } else if (warp < C::FIRST_CONV_WARP) {
         // ------------------------------------------------------------ epilogue
@@ -706,8 +826,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     else
                         mbar_arrive(&acc_empty_bar[acc]);
                 }
-                acc ^= 1;
-                if (acc == 0) acc_phase ^= 1u;
+                if (++acc == acc_bufs) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
             }
             if (!ok) break;
             if (kb0 != 0) {
@@ -962,20 +1084,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         // bf16 tiles (see the layout note below).  Chunk ctid + u * NCT lands u * NCT * 8 bytes
         // further in both layouts (NCT chunks are 16 or 32 whole K-major rows, or half a / a whole
         // MN-major box, and neither changes the XOR terms), so the K loop needs no index math.
-        int hyb_dst0[2];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const bool mn = half ? (args.b_mn_major != 0) : (args.a_mn_major != 0);
-            const int ci = ctid;
-            if (!mn) {
-                const int r = ci >> 3, cp = ci & 7;
-                hyb_dst0[half] = r * 64 + (cp >> 1) * 16 + (((cp ^ r) & 1) << 3);
-            } else {
-                const int box = ci >> 8, kr = (ci & 255) >> 3, c16 = ci & 7;
-                const int lc = (c16 >> 1) ^ (kr & 3);
-                hyb_dst0[half] = box * 2048 + kr * 64 + ((lc ^ ((kr >> 1) & 3)) << 4) + ((c16 & 1) << 3);
-            }
-        }
+        const int hyb_dst0[2] = {hybrid_dst(ctid, args.a_mn_major != 0), hybrid_dst(ctid, args.b_mn_major != 0)};
         for (int seg = 0; seg < n_seg && ok; ++seg) {
             int t, kb0, kb1;
             segment(seg, t, kb0, kb1);
@@ -988,6 +1097,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     ok = false;
                     break;
                 }
+                if (a_tmem) tc_fence_after_sync();  // the MMAs that read this A slot are done (tcgen05.commit)
                 const long long busy0 = clock64();
                 uint4 *raw = reinterpret_cast<uint4 *>(tiles + stage * STAGE_BYTES);
                 uint4 *small = reinterpret_cast<uint4 *>(tiles + SMALL_RING_OFFSET + sstage * STAGE_BYTES);
@@ -1011,40 +1121,80 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     const uint8_t *raw_b = tiles + stage * STAGE_BYTES;
                     uint8_t *out_b = tiles + SMALL_RING_OFFSET + sstage * STAGE_BYTES;
                     constexpr int PER_T = TILE_BYTES / 16 / NCT;  // chunks per thread per operand tile (8 or 4)
+                    if (a_tmem) {
+                        // A operand: this thread owns one row of the A tile -- the row whose tensor
+                        // memory lane its warp can reach (lane quarter = warp % 4) -- and, in the
+                        // one-CTA form with two converter warpgroups, one half of that row's K range.
+                        // It reads the row from the raw tile (undoing the TMA swizzle), splits it, and
+                        // stores bf16(small) and bf16(x), two K elements per 32-bit column, straight
+                        // into the correction MMAs' A slot in tensor memory.
+                        const int q = warp & 3;
+                        const int row = q * 32 + lane;
+                        constexpr int KPARTS = C::NUM_CONV_WARPS / 4;
+                        constexpr int KLEN = BK / KPARTS;
+                        const int kfirst = ((warp - C::FIRST_CONV_WARP) >> 2) * KLEN;
+                        const uint32_t t_slot = tmem_base + a_slot_col0 + static_cast<uint32_t>(sstage * C::A_SLOT_COLS) +
+                                                (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
+                        for (int h = 0; h < KLEN / 16; ++h) {
+                            const int k0 = kfirst + h * 16;
+                            uint32_t w[16];
+                            if (!args.a_mn_major) {
+                                // K-major raw tile: row = 128 bytes, 16-byte chunk c stored at c ^ (row & 7)
+                                const uint8_t *rowp = raw_b + row * 128;
+#pragma unroll
+                                for (int c = 0; c < 4; ++c) {
+                                    const uint4 v = *reinterpret_cast<const uint4 *>(
+                                        rowp + ((((k0 >> 2) + c) ^ (row & 7)) << 4));
+                                    w[4 * c] = v.x;
+                                    w[4 * c + 1] = v.y;
+                                    w[4 * c + 2] = v.z;
+                                    w[4 * c + 3] = v.w;
+                                }
+                            } else {
+                                // MN-major raw tile: boxes of 32 rows (MN) x 32 K; one K index is a
+                                // 128-byte line of 32 MN values whose 32-byte chunks are XORed by (k & 3)
+                                const uint8_t *boxp = raw_b + (row >> 5) * MN_BOX_BYTES + (row & 7) * 4;
+                                const int c32 = (row & 31) >> 3;
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) {
+                                    const int k = k0 + i;
+                                    w[i] = *reinterpret_cast<const uint32_t *>(boxp + k * 128 + ((c32 ^ (k & 3)) << 5));
+                                }
+                            }
+                            uint32_t s8[8], x8[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float f0 = __uint_as_float(w[2 * j]), f1 = __uint_as_float(w[2 * j + 1]);
+                                const float d0 = f0 - __uint_as_float(w[2 * j] & 0xFFFFE000u);
+                                const float d1 = f1 - __uint_as_float(w[2 * j + 1] & 0xFFFFE000u);
+                                const __nv_bfloat162 pp = __floats2bfloat162_rn(d0, d1);
+                                const __nv_bfloat162 qq = __floats2bfloat162_rn(f0, f1);
+                                const uint32_t mm = __heq2_mask(pp, pp);   // zero where Inf / NaN (see below)
+                                s8[j] = *reinterpret_cast<const uint32_t *>(&pp) & mm;
+                                x8[j] = *reinterpret_cast<const uint32_t *>(&qq) & mm;
+                            }
+                            tmem_st_32x8(t_slot + static_cast<uint32_t>(k0 >> 1), s8);
+                            tmem_st_32x8(t_slot + 16u + static_cast<uint32_t>(k0 >> 1), x8);
+                        }
+                        tmem_st_wait();
+                        tc_fence_before_sync();
+                    }
+#pragma unroll
+                    for (int half = a_tmem ? 1 : 0; half < 2; ++half) {
                         const uint4 *rt = reinterpret_cast<const uint4 *>(raw_b + half * TILE_BYTES);
                         uint8_t *s16 = out_b + half * 2 * H_TILE_BYTES;
                         uint8_t *x16 = s16 + H_TILE_BYTES;
+                        // With the extra converter warps at work (pair form), they take the second
+                        // half of the B tile's chunks.
+                        const int n_here = (half == 1 && extra_conv) ? PER_T / 2 : PER_T;
                         uint4 x[PER_T];
 #pragma unroll
-                        for (int u = 0; u < PER_T; ++u) x[u] = rt[ctid + u * NCT];
+                        for (int u = 0; u < PER_T; ++u)
+                            if (u < n_here) x[u] = rt[ctid + u * NCT];
 #pragma unroll
-                        for (int u = 0; u < PER_T; ++u) {
-                            const int dst = hyb_dst0[half] + u * (NCT * 8);
-                            // low part d = x - trunc_tf32(x) (exact) and x itself, rounded to bf16.
-                            // Inf and NaN travel through the TF32 product alone: in the bf16 tiles a
-                            // non-finite element is replaced by zero, otherwise its low part would be
-                            // NaN and 0 x Inf would turn a correction term into NaN where the fp32
-                            // result is +-Inf.  d is NaN exactly for Inf / NaN (Inf - Inf, NaN - NaN),
-                            // so one packed compare of the bf16 pair with itself gives the keep-mask
-                            // of both tiles.
-                            const float f0 = __uint_as_float(x[u].x), f1 = __uint_as_float(x[u].y);
-                            const float f2 = __uint_as_float(x[u].z), f3 = __uint_as_float(x[u].w);
-                            const float d0 = f0 - __uint_as_float(x[u].x & 0xFFFFE000u);
-                            const float d1 = f1 - __uint_as_float(x[u].y & 0xFFFFE000u);
-                            const float d2 = f2 - __uint_as_float(x[u].z & 0xFFFFE000u);
-                            const float d3 = f3 - __uint_as_float(x[u].w & 0xFFFFE000u);
-                            const __nv_bfloat162 p0 = __floats2bfloat162_rn(d0, d1), p1 = __floats2bfloat162_rn(d2, d3);
-                            const __nv_bfloat162 q0 = __floats2bfloat162_rn(f0, f1), q1 = __floats2bfloat162_rn(f2, f3);
-                            const uint32_t m0 = __heq2_mask(p0, p0), m1 = __heq2_mask(p1, p1);
-                            *reinterpret_cast<uint2 *>(s16 + dst) =
-                                make_uint2(*reinterpret_cast<const uint32_t *>(&p0) & m0,
-                                           *reinterpret_cast<const uint32_t *>(&p1) & m1);
-                            *reinterpret_cast<uint2 *>(x16 + dst) =
-                                make_uint2(*reinterpret_cast<const uint32_t *>(&q0) & m0,
-                                           *reinterpret_cast<const uint32_t *>(&q1) & m1);
-                        }
+                        for (int u = 0; u < PER_T; ++u)
+                            if (u < n_here) hybrid_chunk(x[u], s16, x16, hyb_dst0[half] + u * (NCT * 8));
                     }
                 } else if (!(args.dbg & 1))
 #pragma unroll
@@ -1305,6 +1455,8 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
     args.a_mn_major = pl.a_major == kMajorMN;
     args.b_mn_major = pl.b_major == kMajorMN;
     args.terms = opt.terms;
+    args.a_tmem = opt.a_tmem;
+    args.extra_conv = opt.extra_conv;
     args.k_chunk = opt.k_chunk > 0 ? opt.k_chunk : DEFAULT_K_CHUNK;
     if (opt.k_chunk < 0) args.k_chunk = 0;  // whole K inside TMEM (test only)
     args.mask_big = opt.mask_big;
@@ -1340,6 +1492,8 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
                 args.peer_tma = 0;
         }
     }
+    // Warps 2-3 either forward tiles to the peers (fallback form of the fused all-gather) or convert.
+    if (args.n_peers > 0 && !args.peer_tma && args.mc_c == nullptr) args.extra_conv = 0;
     int rc = device_status_ptr(p.device, &args.status);
     if (rc != TTB_OK) return rc;
     args.prof = profile_ptr(p.device);

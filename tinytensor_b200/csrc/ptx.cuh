@@ -370,6 +370,49 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
     }
 }
 
+// Same product with the A operand read from tensor memory instead of shared memory: `a_tmem`
+// addresses 128 lanes (one per row of this CTA's A tile) x 8 columns of 32 bits, each column
+// holding two consecutive K elements (the lower K in the low half).  A in tensor memory is always
+// K-major; B comes from shared memory as before.  With cta_group::2 each CTA of the pair holds
+// its own 128 rows at the same tensor-memory address.
+template <int CG>
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    if constexpr (CG == 1) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P;\n\t"
+            "setp.ne.b32 P, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, P;\n\t"
+            "}"
+            :
+            : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P;\n\t"
+            "setp.ne.b32 P, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, P;\n\t"
+            "}"
+            :
+            : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// Registers -> TMEM: this warp's 32 lanes x 8 consecutive 32-bit columns.  Thread t writes row
+// (lane base + t), columns [col, col + 8).  A warp can only reach the lane quarter given by
+// its index within its warpgroup (warp % 4).
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+                 "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Instruction descriptor for kind::i8: unsigned 8-bit inputs (A/B format 0), s32 accumulate
 // (D format 2), no saturation (bit 3 = 0: sums wrap mod 2^32), both operands K-major.
 // K of one MMA is 32.

@@ -40,6 +40,8 @@ struct Options {
     int conv_columns_mb = 2048;  // budget of conv2d's unrolled-columns workspace
     int int_tensor = 1;          // i32 products may use the int8 tensor-core kernel
     int peer_tma = 1;            // fused all-gather: epilogue tensor stores reach the peers (0: forwarding warps)
+    int a_tmem = 0;              // f32 hybrid split: correction MMAs read their A operands from tensor memory
+    int extra_conv = 1;          // f32 pair form: warps 2-3 convert half of every B tile
 };
 Options g_opt;
 
@@ -411,6 +413,8 @@ static F32Options f32_options(bool two_cta) {
     o.dbg = g_opt.tc_debug;
     o.streamk = g_opt.streamk;
     o.peer_tma = g_opt.peer_tma;
+    o.a_tmem = g_opt.a_tmem;
+    o.extra_conv = g_opt.extra_conv;
     return o;
 }
 
@@ -897,6 +901,14 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         g_opt.int_tensor = value != 0;
         return TTB_OK;
     }
+    if (!strcmp(key, "a_tmem")) {
+        g_opt.a_tmem = value != 0;
+        return TTB_OK;
+    }
+    if (!strcmp(key, "extra_conv")) {
+        g_opt.extra_conv = value != 0;
+        return TTB_OK;
+    }
     if (!strcmp(key, "peer_tma")) {
         g_opt.peer_tma = value != 0;
         return TTB_OK;
@@ -926,6 +938,8 @@ TTB_API int64_t ttb_get_option(const char *key) {
     if (!strcmp(key, "conv_columns_mb")) return g_opt.conv_columns_mb;
     if (!strcmp(key, "int_tensor")) return g_opt.int_tensor;
     if (!strcmp(key, "peer_tma")) return g_opt.peer_tma;
+    if (!strcmp(key, "a_tmem")) return g_opt.a_tmem;
+    if (!strcmp(key, "extra_conv")) return g_opt.extra_conv;
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
