@@ -210,6 +210,43 @@ __device__ __forceinline__ void hybrid_chunk(const uint4 x, uint8_t *s16, uint8_
                                                        *reinterpret_cast<const uint32_t *>(&q1) & m1);
 }
 
+// The same split without the keep-mask, for the common case of finite operands: the caller passes
+// two accumulators that stay finite as long as every element seen was finite (a product of two low
+// parts is finite for finite inputs; the low part of Inf / NaN is NaN, and NaN survives every
+// fused multiply-add after it).  A thread whose accumulators are not finite afterwards converts its
+// chunks again with hybrid_chunk.  This takes the compare and four ANDs per chunk off the ALU pipe,
+// which is the pipe the converter warps keep busiest; the accumulators run on the FMA pipe.
+__device__ __forceinline__ void hybrid_chunk_unmasked(const uint4 x, uint8_t *s16, uint8_t *x16, int dst, float &za,
+                                                      float &zb) {
+    const float f0 = __uint_as_float(x.x), f1 = __uint_as_float(x.y);
+    const float f2 = __uint_as_float(x.z), f3 = __uint_as_float(x.w);
+    const float d0 = f0 - __uint_as_float(x.x & 0xFFFFE000u);
+    const float d1 = f1 - __uint_as_float(x.y & 0xFFFFE000u);
+    const float d2 = f2 - __uint_as_float(x.z & 0xFFFFE000u);
+    const float d3 = f3 - __uint_as_float(x.w & 0xFFFFE000u);
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(d0, d1), p1 = __floats2bfloat162_rn(d2, d3);
+    const __nv_bfloat162 q0 = __floats2bfloat162_rn(f0, f1), q1 = __floats2bfloat162_rn(f2, f3);
+    za = fmaf(d0, d1, za);
+    zb = fmaf(d2, d3, zb);
+    *reinterpret_cast<uint2 *>(s16 + dst) =
+        make_uint2(*reinterpret_cast<const uint32_t *>(&p0), *reinterpret_cast<const uint32_t *>(&p1));
+    *reinterpret_cast<uint2 *>(x16 + dst) =
+        make_uint2(*reinterpret_cast<const uint32_t *>(&q0), *reinterpret_cast<const uint32_t *>(&q1));
+}
+
+// The small slot a converter is about to fill was last read by the MMAs of the K block
+// SMALL_STAGES back.  Their completion arrives on that K block's raw-slot barrier (one
+// tcgen05.commit per K block serves both rings): which barrier that is, and the parity of the
+// phase it completes, from the raw ring's position (stage, phase) of the K block being converted.
+// On the first SMALL_STAGES K blocks the parity names the phase before the barrier's first,
+// which counts as complete.
+__device__ __forceinline__ int small_release_bar(int stage) { return (stage + STAGES - SMALL_STAGES) % STAGES; }
+__device__ __forceinline__ uint32_t small_release_parity(int stage, uint32_t phase) {
+    return stage >= SMALL_STAGES ? phase : (phase ^ 1u);
+}
+
+__device__ __forceinline__ bool all_finite(float za, float zb) { return fabsf(za + zb) <= 3.0e38f; }
+
 // Where the 16-byte chunk `ci` of a raw operand tile goes in the bf16 tiles, from undoing the raw
 // tile's swizzle:
 //  K-major  raw rows are 128 B with 16-B chunks XORed by (row & 7); the bf16 row is 64 B with
@@ -326,9 +363,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 
     extern __shared__ uint8_t smem_dyn[];
     __shared__ uint64_t full_bar[STAGES];   // TMA bytes landed (local)
-    __shared__ uint64_t empty_bar[STAGES];  // MMAs that read the raw slot are done (local)
+    __shared__ uint64_t empty_bar[STAGES];  // the MMAs of the K block in this raw slot are done (local); the
+                                            // converters wait on the same barriers, SMALL_STAGES K blocks back
+    __shared__ uint64_t small_empty_bar[SMALL_STAGES];  // the MMAs that read the small slot are done (local)
     __shared__ uint64_t conv_bar[SMALL_STAGES];         // small tiles written (lives in the leader CTA)
-    __shared__ uint64_t small_empty_bar[SMALL_STAGES];  // MMAs that read the small slot are done (local)
     __shared__ uint64_t acc_full_bar[2];    // accumulator chunk complete (local)
     __shared__ uint64_t acc_empty_bar[2];   // accumulator read out (lives in the leader CTA)
     __shared__ uint64_t out_full_bar[2];    // tile stored into this GPU's C (epilogue -> forwarding warps)
@@ -359,8 +397,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         }
         for (int s = 0; s < SMALL_STAGES; ++s) {
             // converter warps of both CTAs, plus the two extra ones per CTA of the pair form (below)
-            mbar_init(&conv_bar[s], (C::NUM_CONV_WARPS + ((PAIR && args.terms == 2 && args.extra_conv) ? 2 : 0)) * CG);
             mbar_init(&small_empty_bar[s], 1);
+            mbar_init(&conv_bar[s], (C::NUM_CONV_WARPS + ((PAIR && args.terms == 2 && args.extra_conv) ? 2 : 0)) * CG);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full_bar[a], 1);
@@ -568,12 +606,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             const uint32_t idesc16_ts = make_idesc_bf16(C::UMMA_M, C::UMMA_N, 0, args.b_mn_major);
             const uint32_t a16_lbo = args.a_mn_major ? 2048 : 16, a16_kstep = args.a_mn_major ? 1024 : 32;
             const uint32_t b16_lbo = args.b_mn_major ? 2048 : 16, b16_kstep = args.b_mn_major ? 1024 : 32;
-            uint32_t peer_empty[STAGES], peer_small_empty[SMALL_STAGES], peer_acc_full[2];
-            if constexpr (PAIR) {
-                for (int s = 0; s < STAGES; ++s) peer_empty[s] = mapa(smem_u32(&empty_bar[s]), 1);
-                for (int s = 0; s < SMALL_STAGES; ++s) peer_small_empty[s] = mapa(smem_u32(&small_empty_bar[s]), 1);
-                for (int a = 0; a < 2; ++a) peer_acc_full[a] = mapa(smem_u32(&acc_full_bar[a]), 1);
-            }
+            
             for (int seg = 0; seg < n_seg && ok; ++seg) {
                 int t, kb0, kb1;
                 segment(seg, t, kb0, kb1);
@@ -602,12 +635,11 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                             // correction terms on bf16 tiles the converters wrote into the small
                             // slot ([A small | A | B small | B], 8 KiB each).  Half the tensor
                             // cycles of a TF32 correction term, half its shared-memory reads.
-#pragma unroll
-                            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                                const uint32_t fresh = (kb != kb_begin || kk != 0) ? 1u : 0u;
-                                mma_tf32<CG>(d_tmem, make_smem_desc(a_raw + kk * a_kstep, a_lbo, a_sbo, a_swz),
-                                             make_smem_desc(b_raw + kk * b_kstep, b_lbo, b_sbo, b_swz), idesc, fresh);
-                            }
+                            // The corrections go first and the small slot is released right behind
+                            // them: the converters' round trip (slot free -> convert -> converted ->
+                            // issue) then runs while the TF32 product of this K block, which reads
+                            // the raw slot only, keeps the tensor pipe busy.
+                            const uint32_t fresh0 = (kb != kb_begin) ? 1u : 0u;
                             const uint32_t a_s16 = a_small, a_x16 = a_small + H_TILE_BYTES;
                             const uint32_t b_s16 = a_small + 2 * H_TILE_BYTES, b_x16 = a_small + 3 * H_TILE_BYTES;
                             if (a_tmem) {
@@ -618,7 +650,8 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 #pragma unroll
                                 for (int k2 = 0; k2 < BK / 16; ++k2) {
                                     mma_f16_ts<CG>(d_tmem, t_s + k2 * 8,
-                                                   make_smem_desc(b_x16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16_ts, 1);
+                                                   make_smem_desc(b_x16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16_ts,
+                                                   k2 == 0 ? fresh0 : 1u);
                                     mma_f16_ts<CG>(d_tmem, t_x + k2 * 8,
                                                    make_smem_desc(b_s16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16_ts, 1);
                                 }
@@ -626,17 +659,27 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 #pragma unroll
                                 for (int k2 = 0; k2 < BK / 16; ++k2) {
                                     mma_f16<CG>(d_tmem, make_smem_desc(a_s16 + k2 * a16_kstep, a16_lbo, 512, kSwizzle64),
-                                                make_smem_desc(b_x16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16, 1);
+                                                make_smem_desc(b_x16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16,
+                                                k2 == 0 ? fresh0 : 1u);
                                     mma_f16<CG>(d_tmem, make_smem_desc(a_x16 + k2 * a16_kstep, a16_lbo, 512, kSwizzle64),
                                                 make_smem_desc(b_s16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16, 1);
                                 }
                             } else {
-                                // layout check only: bf16(A).bf16(B) on top of the TF32 product
+                                // layout check only: bf16(A).bf16(B) under the TF32 product
 #pragma unroll
                                 for (int k2 = 0; k2 < BK / 16; ++k2)
                                     mma_f16<CG>(d_tmem, make_smem_desc(a_x16 + k2 * a16_kstep, a16_lbo, 512, kSwizzle64),
-                                                make_smem_desc(b_x16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16, 1);
+                                                make_smem_desc(b_x16 + k2 * b16_kstep, b16_lbo, 512, kSwizzle64), idesc16,
+                                                k2 == 0 ? fresh0 : 1u);
                             }
+                            if constexpr (PAIR)
+                                mma_commit_both(smem_u32(&small_empty_bar[sstage]));
+                            else
+                                mma_commit<CG>(smem_u32(&small_empty_bar[sstage]));
+#pragma unroll
+                            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                                mma_tf32<CG>(d_tmem, make_smem_desc(a_raw + kk * a_kstep, a_lbo, a_sbo, a_swz),
+                                             make_smem_desc(b_raw + kk * b_kstep, b_lbo, b_sbo, b_swz), idesc, 1u);
                         } else
 #pragma unroll
                         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
@@ -654,12 +697,17 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                                 mma_tf32<CG>(d_tmem, da_big, db_big, idesc, fresh);
                             }
                         }
-                        mma_commit<CG>(smem_u32(&empty_bar[stage]));
-                        mma_commit<CG>(smem_u32(&small_empty_bar[sstage]));
-                        if constexpr (PAIR) {
-                            mma_commit<CG>(peer_empty[stage]);
-                            mma_commit<CG>(peer_small_empty[sstage]);
+                        // One arrival per barrier reaches both CTAs of a pair.
+                        if (args.terms != 2) {
+                            if constexpr (PAIR)
+                                mma_commit_both(smem_u32(&small_empty_bar[sstage]));
+                            else
+                                mma_commit<CG>(smem_u32(&small_empty_bar[sstage]));
                         }
+                        if constexpr (PAIR)
+                            mma_commit_both(smem_u32(&empty_bar[stage]));
+                        else
+                            mma_commit<CG>(smem_u32(&empty_bar[stage]));
                         if (++stage == STAGES) {
                             stage = 0;
                             phase ^= 1u;
@@ -670,8 +718,10 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                         }
                     }
                     if (!ok) break;
-                    mma_commit<CG>(smem_u32(&acc_full_bar[acc]));
-                    if constexpr (PAIR) mma_commit<CG>(peer_acc_full[acc]);
+                    if constexpr (PAIR)
+                        mma_commit_both(smem_u32(&acc_full_bar[acc]));
+                    else
+                        mma_commit<CG>(smem_u32(&acc_full_bar[acc]));
                     if (++acc == acc_bufs) {
                         acc = 0;
                         acc_phase ^= 1u;
@@ -751,8 +801,13 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     uint4 x[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u) x[u] = rt[(b4 + u) * 64];
+                    float za = 0.0f, zb = 0.0f;
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) hybrid_chunk(x[u], s16, x16, dst0 + (b4 + u) * 512);
+                    for (int u = 0; u < 4; ++u) hybrid_chunk_unmasked(x[u], s16, x16, dst0 + (b4 + u) * 512, za, zb);
+                    if (!all_finite(za, zb)) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) hybrid_chunk(x[u], s16, x16, dst0 + (b4 + u) * 512);
+                    }
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -1192,9 +1247,15 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
 #pragma unroll
                         for (int u = 0; u < PER_T; ++u)
                             if (u < n_here) x[u] = rt[ctid + u * NCT];
+                        float za = 0.0f, zb = 0.0f;
 #pragma unroll
                         for (int u = 0; u < PER_T; ++u)
-                            if (u < n_here) hybrid_chunk(x[u], s16, x16, hyb_dst0[half] + u * (NCT * 8));
+                            if (u < n_here) hybrid_chunk_unmasked(x[u], s16, x16, hyb_dst0[half] + u * (NCT * 8), za, zb);
+                        if (!all_finite(za, zb)) {
+#pragma unroll
+                            for (int u = 0; u < PER_T; ++u)
+                                if (u < n_here) hybrid_chunk(x[u], s16, x16, hyb_dst0[half] + u * (NCT * 8));
+                        }
                     }
                 } else if (!(args.dbg & 1))
 #pragma unroll

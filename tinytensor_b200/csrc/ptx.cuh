@@ -153,6 +153,14 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, ui
         : "r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// The same box brought into L2 only (no shared-memory destination, no completion to wait for):
+// a later tma_load_3d of it then sees L2 latency instead of DRAM latency.
+__device__ __forceinline__ void tma_prefetch_3d(const void *tmap, int32_t c0, int32_t c1, int32_t c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+                 :
+                 : "l"(tmap), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
 // 3-D tiled store this CTA's shared memory -> global (bulk async-group completion).  The box
 // is clipped at the tensor's upper bounds; c0 * elemsize must be a multiple of 16 bytes and no
 // coordinate may be negative.  The shared-memory source must have been written and made
@@ -258,6 +266,17 @@ __device__ __forceinline__ void mma_commit(uint32_t bar_cluster_addr) {
                          bar_cluster_addr)
                      : "memory");
     }
+}
+
+// The same arrival delivered to the barrier at this shared-memory offset in BOTH CTAs of the pair
+// by one instruction (tcgen05.commit's own multicast; no load is involved).
+__device__ __forceinline__ void mma_commit_both(uint32_t bar_addr) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            bar_addr),
+        "h"(mask)
+        : "memory");
 }
 
 // TMEM -> registers: this warp's 32 lanes x 32 consecutive fp32 columns.
