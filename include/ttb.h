@@ -355,7 +355,8 @@ TTB_API const char *ttb_variant_name(int variant);
  * test only), "two_cta" (automatic dispatch: -1 = pick the CTA-pair kernel by
  * shape, default; 0 = never; 1 = always),
  * "splitk" (0 = never split K in the SIMT kernel), "mask_big" (test only),
- * "tc_profile" (1 = record wait-cycle counters, see ttb_tc_profile),
+ * "tc_profile" (1 = record wait-cycle counters, see ttb_tc_profile; 2 = the CTA lifetimes only, which
+ *              costs the kernel nothing),
  * "streamk" (f32 tensor-core kernel: deal the K blocks of all tiles out evenly
  * over the SMs instead of whole tiles; -1 = when whole tiles would leave SMs
  * idle, default; 0 = never; 1 = whenever possible),

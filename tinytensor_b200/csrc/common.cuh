@@ -67,6 +67,7 @@ int sm_count(int device, int *out);
 // Device buffer for the tcgen05 kernel's wait-cycle counters, or nullptr when the
 // "tc_profile" option is off.
 long long *profile_ptr(int device);
+int profile_level();  // 0 off, 1 all counters, 2 the CTA lifetimes only (no clock reads inside the loops)
 // Stream-K workspace (partial-sum slots, ready flags) of (device, stream).
 int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags);
 

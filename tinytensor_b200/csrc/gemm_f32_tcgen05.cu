@@ -356,7 +356,9 @@ __device__ __forceinline__ void forward_tile(const TcArgs &args, int t, int cta_
     }
 }
 
-template <int CG>
+// PROF: the roles count the cycles they wait and work (ttb_tc_profile); the clock reads cost each
+// role a few dozen cycles per K block, so the counting build is a kernel of its own.
+template <int CG, bool PROF>
 __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kernel(const __grid_constant__ TcArgs args) {
     using C = Cfg<CG>;
     constexpr bool PAIR = CG == 2;
@@ -377,7 +379,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     __shared__ int seg_tile_s[kMaxSegments], seg_kb0_s[kMaxSegments], seg_kb1_s[kMaxSegments], seg_count_s;
     __shared__ int abort_flag_s;
 
-    const long long kernel_t0 = clock64();
+    const long long kernel_t0 = args.prof ? clock64() : 0;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
@@ -521,7 +523,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 const int m0 = tm * C::TILE_M + static_cast<int>(cta_rank) * BM;
                 const int n0 = tn * C::TILE_N + static_cast<int>(cta_rank) * BNC;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!wait_or_abort<PAIR>(&empty_bar[stage], phase ^ 1u, abort_flag, &w_a)) {
+                    if (!wait_or_abort<PAIR>(&empty_bar[stage], phase ^ 1u, abort_flag, PROF ? &w_a : nullptr)) {
                         report(args.status, abort_flag, kErrProducerWait, static_cast<unsigned>(stage));
                         ok = false;
                         break;
@@ -569,7 +571,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 for (int i = 0; i < 100000; ++i)
                     if (mbar_try_wait(&full_bar[last], last_phase)) break;
             }
-            if (args.prof) args.prof[blockIdx.x * kProfSlots + kProfProducerEmpty] = w_a;
+            if (PROF && args.prof) args.prof[blockIdx.x * kProfSlots + kProfProducerEmpty] = w_a;
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -611,7 +613,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 int t, kb0, kb1;
                 segment(seg, t, kb0, kb1);
                 for (int kb_begin = kb0; kb_begin < kb1 && ok; kb_begin += k_chunk) {
-                    if (!wait_or_abort<PAIR>(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, &w_a)) {
+                    if (!wait_or_abort<PAIR>(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, PROF ? &w_a : nullptr)) {
                         report(args.status, abort_flag, kErrAccEmptyWait, static_cast<unsigned>(acc));
                         ok = false;
                         break;
@@ -620,7 +622,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * C::ACC_COLS);
                     const int kb_end = (kb_begin + k_chunk < kb1) ? kb_begin + k_chunk : kb1;
                     for (int kb = kb_begin; kb < kb_end; ++kb) {
-                        if (!wait_or_abort<PAIR>(&conv_bar[sstage], sphase, abort_flag, &w_b)) {
+                        if (!wait_or_abort<PAIR>(&conv_bar[sstage], sphase, abort_flag, PROF ? &w_b : nullptr)) {
                             report(args.status, abort_flag, kErrMmaWait, static_cast<unsigned>(stage));
                             ok = false;
                             break;
@@ -732,7 +734,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             mma_commit<CG>(smem_u32(&drain_bar));
             for (int i = 0; i < 1000000; ++i)
                 if (mbar_try_wait(&drain_bar, 0)) break;
-            if (args.prof) {
+            if (PROF && args.prof) {
                 args.prof[blockIdx.x * kProfSlots + kProfMmaAccEmpty] = w_a;
                 args.prof[blockIdx.x * kProfSlots + kProfMmaConv] = w_b;
             }
@@ -853,7 +855,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             int b, tm, tn;
             tile_coords(t, args.tiles_m, args.tiles_n, b, tm, tn);
             for (int ch = kb0; ch < kb1; ch += k_chunk) {
-                if (!wait_or_abort<PAIR>(&acc_full_bar[acc], acc_phase, abort_flag, &w_a)) {
+                if (!wait_or_abort<PAIR>(&acc_full_bar[acc], acc_phase, abort_flag, PROF ? &w_a : nullptr)) {
                     if (lane == 0) report(args.status, abort_flag, kErrEpilogueWait, static_cast<unsigned>(acc));
                     ok = false;
                     break;
@@ -1116,7 +1118,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             if (args.n_peers > 0 || args.mc_c != nullptr) __threadfence_system();
         }
         if (args.prof && warp == C::FIRST_EPI_WARP && lane == 0) {
-            args.prof[blockIdx.x * kProfSlots + kProfEpiAccFull] = w_a;
+            if (PROF) args.prof[blockIdx.x * kProfSlots + kProfEpiAccFull] = w_a;
             args.prof[blockIdx.x * kProfSlots + kProfTotal] = clock64() - kernel_t0;
         }
     } else {
@@ -1146,14 +1148,14 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
             for (int kb = kb0; kb < kb1; ++kb) {
                 // The small slot must have been released by the MMAs that last read it, and the
                 // raw slot must have landed.
-                if (!wait_or_abort<PAIR>(&small_empty_bar[sstage], sphase ^ 1u, abort_flag, &w_a) ||
-                    !wait_or_abort<false>(&full_bar[stage], phase, abort_flag, &w_b)) {
+                if (!wait_or_abort<PAIR>(&small_empty_bar[sstage], sphase ^ 1u, abort_flag, PROF ? &w_a : nullptr) ||
+                    !wait_or_abort<false>(&full_bar[stage], phase, abort_flag, PROF ? &w_b : nullptr)) {
                     if (lane == 0) report(args.status, abort_flag, kErrConverterWait, static_cast<unsigned>(stage));
                     ok = false;
                     break;
                 }
                 if (a_tmem) tc_fence_after_sync();  // the MMAs that read this A slot are done (tcgen05.commit)
-                const long long busy0 = clock64();
+                const long long busy0 = PROF ? clock64() : 0;
                 uint4 *raw = reinterpret_cast<uint4 *>(tiles + stage * STAGE_BYTES);
                 uint4 *small = reinterpret_cast<uint4 *>(tiles + SMALL_RING_OFFSET + sstage * STAGE_BYTES);
                 // All loads of a batch are issued before the first dependent instruction, so
@@ -1289,7 +1291,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     else
                         mbar_arrive(&conv_bar[sstage]);
                 }
-                w_c += clock64() - busy0;
+                if constexpr (PROF) w_c += clock64() - busy0;
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
@@ -1300,7 +1302,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 }
             }
         }
-        if (args.prof && ctid == 0) {
+        if (PROF && args.prof && ctid == 0) {
             args.prof[blockIdx.x * kProfSlots + kProfConvSmallEmpty] = w_a;
             args.prof[blockIdx.x * kProfSlots + kProfConvFull] = w_b;
             args.prof[blockIdx.x * kProfSlots + kProfConvBusy] = w_c;
@@ -1375,15 +1377,16 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     args.total_tiles = args.tiles_m * args.tiles_n * args.B;
     // Per-device launch set-up, done once; several host threads may arrive here together.
     static std::mutex setup_mu;
-    static bool attr_set[64] = {false};
+    static bool attr_set[2][64] = {{false}};
     static int max_clusters[64] = {0};
-    auto kernel = gemm_f32_3xtf32_kernel<CG>;
+    const int prof = (args.prof != nullptr && profile_level() == 1) ? 1 : 0;
+    auto kernel = prof ? gemm_f32_3xtf32_kernel<CG, true> : gemm_f32_3xtf32_kernel<CG, false>;
     {
         std::lock_guard<std::mutex> lk(setup_mu);
-        if (!attr_set[p.device & 63]) {
+        if (!attr_set[prof][p.device & 63]) {
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
             if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
-            attr_set[p.device & 63] = true;
+            attr_set[prof][p.device & 63] = true;
         }
     }
     cudaLaunchConfig_t cfg{};

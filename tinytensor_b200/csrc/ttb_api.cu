@@ -164,6 +164,8 @@ long long *profile_ptr(int device) {
     return d->prof;
 }
 
+int profile_level() { return g_opt.tc_profile; }
+
 size_t conv_columns_budget() { return static_cast<size_t>(g_opt.conv_columns_mb) << 20; }
 
 int sm_count(int device, int *out) {
@@ -882,7 +884,7 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         return TTB_OK;
     }
     if (!strcmp(key, "tc_profile")) {
-        g_opt.tc_profile = value != 0;
+        g_opt.tc_profile = value == 2 ? 2 : (value != 0 ? 1 : 0);
         return TTB_OK;
     }
     if (!strcmp(key, "streamk")) {
