@@ -245,6 +245,31 @@ def check_against_float64(torch, A, B, C, rows, cols) -> float:
     return err / scale
 
 
+_T0 = time.perf_counter()
+
+
+_PHASE = ["start"]
+
+
+def watchdog(seconds: float) -> None:
+    """Ends the process with a message naming the phase it was in if the run outlives `seconds`:
+    a wait on another rank that never comes must not hold the GPUs until someone else's limit."""
+    def run():
+        time.sleep(seconds)
+        print(f"[bench rank {os.environ.get('RANK', '0')}] gave up after {seconds:.0f} s in phase: {_PHASE[0]}",
+              file=sys.stderr, flush=True)
+        os._exit(3)
+    threading.Thread(target=run, daemon=True).start()
+
+
+def progress(msg: str) -> None:
+    """One line per phase on stderr (stdout carries only the JSON line): a run that is cut short
+    still shows how far every rank got."""
+    _PHASE[0] = "after: " + msg
+    print(f"[bench rank {os.environ.get('RANK', '0')} +{time.perf_counter() - _T0:7.1f}s] {msg}", file=sys.stderr,
+          flush=True)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -262,6 +287,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ttb.lib()  # fail loudly if the extension is missing
+    progress("process group up, library loaded")
     peaks, peak_kind = measured_peaks()
 
     # Operands, drawn on the host as a tinytensor program draws them (Generator(3), normal) and
@@ -270,6 +296,7 @@ def run_ours(args):
     hA = torch.from_numpy(ops["A"]).unsqueeze(0).pin_memory()
     hB = torch.from_numpy(ops["B"]).unsqueeze(0).pin_memory()
     A, B = hA.to(dev), hB.to(dev)
+    progress("operands drawn and uploaded")
     fused = args.exchange in ("fused", "fused-peer", "fused-multicast")
     sharded = ttb.ShardedMatmul(exchange={"fused": "peer", "fused-peer": "peer", "fused-multicast": "multicast"}.get(
         args.exchange, "auto")) if world > 1 else None
@@ -321,7 +348,11 @@ def run_ours(args):
             else:
                 step(i)
         stop.record()
+        if n_steps > 100:
+            progress(f"{n_steps} steps queued")
         barrier()
+        if n_steps > 100:
+            progress("ranks met after the loop")
         clocks = sampler.stop(t_begin, time.perf_counter())
         ms = start.elapsed_time(stop) / n_steps
         kernel = sum(a.elapsed_time(b) for a, b in ev) / n_steps if ev is not None else None
@@ -329,15 +360,24 @@ def run_ours(args):
 
     for i in range(max(args.warmup, 3)):
         step(i)
+    progress("warm-up done")
     launches0 = ttb.launch_count()
     ms_per_step, kernel_ms, clocks = timed_loop(args.steps, True)
     launches = ttb.launch_count() - launches0
     variant = ttb.last_variant().name
+    progress(f"timed loop done: {ms_per_step:.3f} ms per step")
     ttb.check_device(local_rank)
 
     # The same step for at least two seconds without a pause: the power-capped regime.
-    sustained_steps = int(max(args.steps, min(4000, 2200.0 / max(ms_per_step, 1e-3))))
+    # (the step count must be the same on every rank: each step meets the other ranks at a barrier)
+    ms_all = ms_per_step
+    if world > 1:
+        t = torch.tensor([ms_per_step], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_all = float(t.item())
+    sustained_steps = int(max(args.steps, min(4000, 2200.0 / max(ms_all, 1e-3))))
     sus_ms, _, sus_clocks = timed_loop(sustained_steps, False)
+    progress(f"sustained loop done: {sus_ms:.3f} ms per step over {sustained_steps} steps")
     ttb.check_device(local_rank)
 
     # ---- verification, untimed, on every rank
@@ -355,6 +395,7 @@ def run_ours(args):
     B.copy_(hB)
     torch.cuda.synchronize()
     max_err = max(errs)
+    progress(f"parity checked: {max_err:.2e}")
 
     # ---- breakdown of a step at N > 1 (each piece timed alone, same events method)
     breakdown = None
@@ -394,6 +435,7 @@ def run_ours(args):
         ttb.check_device(local_rank)
 
     # ---- end to end: operands in pinned host memory, result back in host memory, every step
+    progress("breakdown done")
     e2e_steps = max(1, min(args.steps, 5))
     if world == 1:
         hC = torch.empty((1, DIM, DIM), dtype=torch.float32, pin_memory=True)
@@ -420,6 +462,7 @@ def run_ours(args):
         run_e2e()
     barrier()
     e2e_s = time.perf_counter() - t0
+    progress(f"end-to-end loop done: {e2e_s / e2e_steps * 1e3:.1f} ms per step")
     e2e_err = None
     if world == 1:
         e2e_err = check_against_float64(torch, A, B, hC.to(dev), rows[:6], cols[:6])
@@ -493,6 +536,7 @@ def run_ours(args):
         rec, _ = bench_configs.measure(name, torch, dist, ttb, dev, world, rank, 10, peaks, peak_kind, fp64_peak,
                                        with_graph=(name in ("c1", "c3")), with_e2e=False)
         other[name] = rec
+        progress(f"configuration {name} measured")
     if world > 1:
         dist.barrier()
 
@@ -597,7 +641,10 @@ def main():
                          "are the callers either side of the path (bench_callers.py)")
     ap.add_argument("--skip-other-configs", action="store_true",
                     help="c4 only: leave the other BASELINE configurations out of the line")
+    ap.add_argument("--deadline", type=float, default=900.0,
+                    help="seconds after which the process ends itself, naming the phase it was in")
     args = ap.parse_args()
+    watchdog(args.deadline)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload in ("conv", "linear"):
