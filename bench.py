@@ -298,7 +298,7 @@ def run_ours(args):
     A, B = hA.to(dev), hB.to(dev)
     progress("operands drawn and uploaded")
     fused = args.exchange in ("fused", "fused-peer", "fused-multicast")
-    sharded = ttb.ShardedMatmul(exchange={"fused": "peer", "fused-peer": "peer", "fused-multicast": "multicast"}.get(
+    sharded = ttb.ShardedMatmul(exchange={"fused": "auto", "fused-peer": "peer", "fused-multicast": "multicast"}.get(
         args.exchange, "auto")) if world > 1 else None
     # Two C buffers used in turn.  At N > 1 with the fused exchange they live in symmetric memory:
     # the GEMM kernel itself stores each finished tile into every rank's C over NVLink, and a

@@ -372,6 +372,11 @@ TTB_API const char *ttb_variant_name(int variant);
  * faster, the pair form then has room for one accumulator only),
  * "extra_conv" (1, default: the two spare warps of the f32 pair kernel convert half of every
  * rhs tile; 0: converter warpgroup only),
+ * "pieces" (-1 / 0, default: off; n >= 2: the f32 tensor-core kernel cuts every tile's K range into
+ * the largest power of two of equal parts not above n and deals the parts out round-robin, so
+ * that tiles complete all through the kernel; the part that arrives last adds all parts in part
+ * order, so results do not depend on timing -- measured: the hand-overs cost 15 % and more, so
+ * nothing selects it by itself),
  * "tc_debug" (bit mask of timing / fault-handling experiments of the f32
  * tensor-core kernel, test only: results are wrong or absent when set).
  * Returns TTB_EINVAL for an unknown key or value. */

@@ -311,3 +311,28 @@ def test_converter_variants_meet_f32_tolerance_all_layouts(forced, shape, option
     finally:
         forced.set_option("a_tmem", 0)
         forced.set_option("extra_conv", 1)
+
+
+@pytest.mark.parametrize("pieces", [2, 4, 8])
+@pytest.mark.parametrize("shape", [(1, 1024, 2048, 768), (3, 300, 1504, 260), (1, 512, 4096, 512)])
+def test_piece_schedule_meets_f32_tolerance_and_is_repeatable(forced, shape, pieces):
+    """The piece schedule (every tile's K range cut into a power of two of parts that are dealt out
+    round-robin; the part that draws a tile's last ticket adds all parts in part order): same
+    tolerance as whole tiles, and the same bits on every run whichever part comes last."""
+    rng = np.random.default_rng(91)
+    B, N, K, M = shape
+    a = dev(rng.standard_normal((B, N, K)).astype(np.float32))
+    b = dev(rng.standard_normal((B, K, M)).astype(np.float32))
+    want = np.matmul(host(a).astype(np.float64), host(b).astype(np.float64))
+    if forced.get_option("force_variant") == int(forced.Variant.TCGEN05_2CTA) and (N <= 128 or M <= 128):
+        pytest.skip("pair tiles need both extents above 128")
+    forced.set_option("pieces", pieces)
+    try:
+        first = host(forced.batched_matmul(a, b))
+        assert rel_to_max(first, want) <= F32_TOL
+        for _ in range(3):
+            again = host(forced.batched_matmul(a, b))
+            assert np.array_equal(first, again)
+        forced.check_device(0)
+    finally:
+        forced.set_option("pieces", -1)

@@ -70,6 +70,8 @@ long long *profile_ptr(int device);
 int profile_level();  // 0 off, 1 all counters, 2 the CTA lifetimes only (no clock reads inside the loops)
 // Stream-K workspace (partial-sum slots, ready flags) of (device, stream).
 int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigned int **flags);
+// The flags array holds 2 x 8 x SMs slot flags followed by this many arrival counters.
+constexpr int kStreamKTickets = 65536;
 
 // Per-dtype launchers.  Each returns a ttb_status.
 // allow_skinny: products with one tiny dim may take the streaming kernels (automatic dispatch).
@@ -85,6 +87,8 @@ struct F32Options {
     int peer_tma = 1;   // fused all-gather: peers are reached by the epilogue's bulk tensor stores when possible
     int a_tmem = 0;     // hybrid split: A operands of the correction MMAs in tensor memory
     int extra_conv = 1; // pair form: the two spare warps of the producer warpgroup convert too
+    int pieces = -1;    // piece schedule (every tile's K cut into this many parts, dealt out round-robin):
+                        // -1 = four parts when an all-gather is fused into the product, 0 = never
 };
 // n_peers > 0 fuses an all-gather into the product: every finished tile is also stored into
 // peer_c[i] (peer-mapped pointers to the other GPUs' C, same layout as p.c).

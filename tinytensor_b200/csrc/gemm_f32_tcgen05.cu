@@ -135,6 +135,18 @@ struct alignas(64) TcArgs {
     int sk_tile0;  // stream-K: tiles [0, sk_tile0) stay whole; the rest is cut by K blocks
     float *sk_partials;       // stream-K workspace: per unit, CTA and epilogue warp 32 x 128 partial sums
     unsigned int *sk_flags;   // stream-K flags, one per unit, CTA and epilogue warp: 1 while partial sums wait
+    // Piece schedule (pieces > 1, instead of streamk): every tile's K range is cut into `pieces`
+    // parts (a power of two) of piece_len K blocks, the parts are dealt out round-robin (part
+    // g = unit + i * units belongs to tile g / pieces), so the parts of a tile run at the same time on neighbouring
+    // units and `units / pieces` tiles complete every piece_len K blocks, all through the kernel,
+    // instead of one tile per unit at the very end.  The fused all-gather wants that: the
+    // exchange of a completed tile overlaps the parts that follow, and only the last few tiles'
+    // exchange is exposed.  Every part writes its sums to a slot of the stream-K workspace (two
+    // per unit, used in turn) and takes a ticket of its tile; the part that takes the last
+    // ticket adds all parts in part order (its own included, read back, so that the result does
+    // not depend on which part came last), lowers their flags and stores the tile.
+    int pieces, pieces_log2, piece_len;
+    unsigned int *sk_tickets;  // arrival counters, one per tile, CTA and epilogue warp; 0 between launches
     int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
     float *mc_c;   // fused all-gather through an NVLink multicast address of C (same offset and strides
                    // as `c`): one multimem.st reaches every GPU, this one included; nullptr = off
@@ -412,7 +424,21 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         }
         mbar_init(&last_full_bar, 4 * C::EPI_WGS);
         mbar_init(&drain_bar, 1);
-        if (args.streamk) {
+        if (args.pieces > 1) {
+            // piece schedule (the host sets streamk with it): parts u, u + units, ... of all tiles' parts
+            const int nkb = (args.K + BK - 1) / BK;
+            const int u = PAIR ? (blockIdx.x >> 1) : blockIdx.x, us = PAIR ? (gridDim.x >> 1) : gridDim.x;
+            const int total = args.total_tiles << args.pieces_log2;
+            int n = 0;
+            for (int g = u; g < total && n < kMaxSegments; g += us) {
+                const int k0 = (g & (args.pieces - 1)) * args.piece_len;
+                seg_tile_s[n] = g >> args.pieces_log2;
+                seg_kb0_s[n] = k0;
+                seg_kb1_s[n] = k0 + args.piece_len < nkb ? k0 + args.piece_len : nkb;
+                ++n;
+            }
+            seg_count_s = n;
+        } else if (args.streamk) {
             // cut this unit's K-block range into per-tile segments
             const int nkb = (args.K + BK - 1) / BK;
             const int u = PAIR ? (blockIdx.x >> 1) : blockIdx.x, us = PAIR ? (gridDim.x >> 1) : gridDim.x;
@@ -889,7 +915,90 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 }
             }
             if (!ok) break;
-            if (kb0 != 0) {
+            if (args.pieces > 1) {
+                // Piece schedule: write this part's sums, draw a ticket; the last one in adds up.
+                const int P = args.pieces, PL = args.pieces_log2;
+                const long long my_slot =
+                    ((static_cast<long long>(unit) * 2 + (seg & 1)) * CG + cta_rank) * EPI_WARPS + epi_warp;
+                // The slot was last used two parts ago; whoever completed that tile has lowered
+                // its flag long since, unless that unit fell far behind.
+                unsigned long long t0 = 0;
+                for (uint32_t spin = 0;; ++spin) {
+                    if (*reinterpret_cast<volatile unsigned int *>(&args.sk_flags[my_slot]) == 0u) break;
+                    if ((spin & 63u) == 63u) {
+                        const unsigned long long now = global_ns();
+                        if (t0 == 0) t0 = now;
+                        if (*abort_flag || now - t0 > 2000000000ull) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+                if (!ok) {
+                    if (lane == 0) report(args.status, abort_flag, kErrStreamKWait, 0x10000u + static_cast<unsigned>(unit));
+                    break;
+                }
+                float4 *dst = reinterpret_cast<float4 *>(args.sk_partials + my_slot * 4096) + lane;
+#pragma unroll
+                for (int q = 0; q < 32; ++q)
+                    dst[q * 32] = make_float4(sum[4 * q], sum[4 * q + 1], sum[4 * q + 2], sum[4 * q + 3]);
+                __threadfence();
+                __syncwarp();
+                unsigned int ticket = 0;
+                const long long tk = (static_cast<long long>(t) * CG + cta_rank) * EPI_WARPS + epi_warp;
+                if (lane == 0) {
+                    atomicExch(&args.sk_flags[my_slot], 1u);
+                    __threadfence();
+                    ticket = atomicAdd(&args.sk_tickets[tk], 1u);
+                }
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket != static_cast<unsigned int>(P - 1)) continue;
+                __threadfence();
+                // Part 0 replaces the registers, the others are added, in part order.
+                {
+                    const int gj = t << PL;
+                    const int uj = gj % units, sj = gj / units;
+                    const long long slot = ((static_cast<long long>(uj) * 2 + (sj & 1)) * CG + cta_rank) * EPI_WARPS + epi_warp;
+                    const float4 *src = reinterpret_cast<const float4 *>(args.sk_partials + slot * 4096) + lane;
+#pragma unroll
+                    for (int v0 = 0; v0 < 32; v0 += 8) {
+                        float4 pv[8];
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) pv[v] = __ldcg(src + (v0 + v) * 32);
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            sum[4 * (v0 + v)] = pv[v].x;
+                            sum[4 * (v0 + v) + 1] = pv[v].y;
+                            sum[4 * (v0 + v) + 2] = pv[v].z;
+                            sum[4 * (v0 + v) + 3] = pv[v].w;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) args.sk_flags[slot] = 0u;  // consumed
+                }
+                for (int j = 1; j < P; ++j) {
+                    const int gj = (t << PL) + j;
+                    const int uj = gj % units, sj = gj / units;
+                    const long long slot = ((static_cast<long long>(uj) * 2 + (sj & 1)) * CG + cta_rank) * EPI_WARPS + epi_warp;
+                    const float4 *src = reinterpret_cast<const float4 *>(args.sk_partials + slot * 4096) + lane;
+#pragma unroll
+                    for (int v0 = 0; v0 < 32; v0 += 8) {
+                        float4 pv[8];
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) pv[v] = __ldcg(src + (v0 + v) * 32);
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            sum[4 * (v0 + v)] += pv[v].x;
+                            sum[4 * (v0 + v) + 1] += pv[v].y;
+                            sum[4 * (v0 + v) + 2] += pv[v].z;
+                            sum[4 * (v0 + v) + 3] += pv[v].w;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) args.sk_flags[slot] = 0u;  // consumed
+                }
+                if (lane == 0) args.sk_tickets[tk] = 0u;  // ready for the next launch
+            } else if (kb0 != 0) {
                 // Stream-K, a range that starts inside a tile: hand the partial sums to the unit
                 // that owns the tile.  Warp w of the owner reads exactly what warp w wrote here
                 // (same TMEM lanes, same columns), so one flag per warp is all the ordering needed.
@@ -907,8 +1016,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 // graph replays correctly.
                 if (lane == 0) atomicExch(&args.sk_flags[slot], 1u);
                 continue;
-            }
-            if (kb1 != num_kb) {
+            } else if (kb1 != num_kb) {
                 // Stream-K, the owner of a tile whose tail other units computed: add their sums.
                 const long long all_kb = static_cast<long long>(args.total_tiles - args.sk_tile0) * num_kb;
                 for (int q = unit + 1; q < units && ok; ++q) {
@@ -1370,7 +1478,7 @@ bool plan(const Problem &p, TcPlan *pl, char *why, int why_len) {
 }
 
 template <int CG>
-int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
+int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt, int pieces_opt) {
     using C = Cfg<CG>;
     args.tiles_m = static_cast<int>((p.N + C::TILE_M - 1) / C::TILE_M);
     args.tiles_n = static_cast<int>((p.M + C::TILE_N - 1) / C::TILE_N);
@@ -1463,6 +1571,48 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt) {
     }
     args.streamk = streamk ? 1 : 0;
     if (!streamk && units > args.total_tiles) units = args.total_tiles;
+    // Piece schedule instead (see TcArgs): wanted when tiles should complete all through the
+    // kernel, i.e. with an all-gather fused into the product that the epilogue itself sends.
+    args.pieces = 0;
+    {
+        const bool sends = (args.n_peers > 0 && args.peer_tma) || args.mc_c != nullptr;
+        int want = pieces_opt < 0 ? 0 : pieces_opt;  // measured: the hand-overs cost more than the spread-out exchange gains
+        (void)sends;
+        if (args.n_peers > 0 && !args.peer_tma && args.mc_c == nullptr) want = 0;  // forwarding warps count stores ahead
+        const int kc = args.k_chunk > 0 ? args.k_chunk : 1;
+        if (want > 1 && num_kb >= 2 * kc && args.total_tiles > 0 &&
+            static_cast<long long>(args.total_tiles) * CG * 8 <= kStreamKTickets) {
+            // a power of two of equal non-empty parts, each a whole number of accumulation chunks
+            int lg = 0;
+            while ((2 << lg) <= want) ++lg;
+            long long len = 0, parts = 0;
+            int pu = sms / CG;
+            if (CG == 2 && pu > max_clusters[p.device & 63]) pu = max_clusters[p.device & 63];
+            for (; lg > 0; --lg) {
+                len = (num_kb + (1 << lg) - 1) >> lg;
+                len = (len + kc - 1) / kc * kc;
+                parts = (num_kb + len - 1) / len;
+                // equal parts, and a unit's list of parts must fit the kernel's segment table
+                if (parts == (1 << lg) && (args.total_tiles * parts + pu - 1) / pu <= kMaxSegments) break;
+            }
+            if (lg > 0 && args.total_tiles * parts < 0x7FFFFFFFLL) {
+                args.pieces_log2 = lg;
+                int rc = TTB_OK;
+                if (!streamk) rc = streamk_workspace(p.device, p.stream, &args.sk_partials, &args.sk_flags);
+                if (rc == TTB_OK) {
+                    args.pieces = static_cast<int>(parts);
+                    args.piece_len = static_cast<int>(len);
+                    args.sk_tickets = args.sk_flags + static_cast<size_t>(sms) * 16;
+                    args.streamk = 1;   // the kernel reads its parts from the segment table, as for stream-K
+                    units = sms / CG;
+                    if (CG == 2 && units > max_clusters[p.device & 63]) units = max_clusters[p.device & 63];
+                    if (units > args.total_tiles * parts) units = static_cast<int>(args.total_tiles * parts);
+                } else {
+                    set_error("%s", "");
+                }
+            }
+        }
+    }
     cfg.gridDim = dim3(static_cast<unsigned>(units * CG));
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
     if (e != cudaSuccess) return cuda_fail(e, "gemm_f32_3xtf32_kernel launch");
@@ -1564,8 +1714,8 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
     args.dbg = opt.dbg;
     int sms = 148;
     sm_count(p.device, &sms);
-    if (opt.two_cta) return launch_cg<2>(p, args, sms, opt.streamk);
-    return launch_cg<1>(p, args, sms, opt.streamk);
+    if (opt.two_cta) return launch_cg<2>(p, args, sms, opt.streamk, opt.pieces);
+    return launch_cg<1>(p, args, sms, opt.streamk, opt.pieces);
 }
 
 }  // namespace ttb

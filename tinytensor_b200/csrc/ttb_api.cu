@@ -42,6 +42,7 @@ struct Options {
     int peer_tma = 1;            // fused all-gather: epilogue tensor stores reach the peers (0: forwarding warps)
     int a_tmem = 0;              // f32 hybrid split: correction MMAs read their A operands from tensor memory
     int extra_conv = 1;          // f32 pair form: warps 2-3 convert half of every B tile
+    int pieces = -1;             // f32 tensor-core kernel: piece schedule (-1 automatic, 0 never, n parts per tile)
 };
 Options g_opt;
 
@@ -198,16 +199,18 @@ int streamk_workspace(int device, cudaStream_t stream, float **partials, unsigne
     }
     StreamKSet s{};
     s.stream = stream;
-    // One 32 x 128 fp32 slot per epilogue warp: at most 8 warps per SM's CTA.
-    const size_t slots = static_cast<size_t>(d->sms) * 8;
+    // 32 x 128 fp32 slots, two per epilogue warp (at most 8 warps per SM's CTA): the contiguous
+    // cut uses the first of each pair, the piece schedule both in turn.  Behind the slot flags,
+    // kStreamKTickets arrival counters for the piece schedule (one per tile, CTA and warp).
+    const size_t slots = static_cast<size_t>(d->sms) * 8 * 2;
     cudaError_t e = cudaMalloc(&s.partials, slots * 32 * 128 * sizeof(float));
     if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(stream-K partials)");
-    e = cudaMalloc(&s.flags, slots * sizeof(unsigned int));
+    e = cudaMalloc(&s.flags, (slots + kStreamKTickets) * sizeof(unsigned int));
     if (e != cudaSuccess) {
         cudaFree(s.partials);
         return cuda_fail(e, "cudaMalloc(stream-K flags)");
     }
-    e = cudaMemset(s.flags, 0, slots * sizeof(unsigned int));
+    e = cudaMemset(s.flags, 0, (slots + kStreamKTickets) * sizeof(unsigned int));
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(stream-K flags)");
     d->sk[d->sk_count++] = s;
     *partials = s.partials;
@@ -417,6 +420,7 @@ static F32Options f32_options(bool two_cta) {
     o.peer_tma = g_opt.peer_tma;
     o.a_tmem = g_opt.a_tmem;
     o.extra_conv = g_opt.extra_conv;
+    o.pieces = g_opt.pieces;
     return o;
 }
 
@@ -907,6 +911,14 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         g_opt.a_tmem = value != 0;
         return TTB_OK;
     }
+    if (!strcmp(key, "pieces")) {
+        if (value < -1 || value > 64) {
+            set_error("pieces out of range (-1 automatic, 0 never, up to 64 parts per tile)");
+            return TTB_EINVAL;
+        }
+        g_opt.pieces = static_cast<int>(value);
+        return TTB_OK;
+    }
     if (!strcmp(key, "extra_conv")) {
         g_opt.extra_conv = value != 0;
         return TTB_OK;
@@ -942,6 +954,7 @@ TTB_API int64_t ttb_get_option(const char *key) {
     if (!strcmp(key, "peer_tma")) return g_opt.peer_tma;
     if (!strcmp(key, "a_tmem")) return g_opt.a_tmem;
     if (!strcmp(key, "extra_conv")) return g_opt.extra_conv;
+    if (!strcmp(key, "pieces")) return g_opt.pieces;
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
