@@ -287,6 +287,9 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ttb.lib()  # fail loudly if the extension is missing
+    for kv in args.ttb_option:
+        key, _, val = kv.partition("=")
+        ttb.set_option(key, int(val))
     progress("process group up, library loaded")
     peaks, peak_kind = measured_peaks()
 
@@ -584,6 +587,7 @@ def run_ours(args):
                                        "used in turn")
                        if world > 1 else "single GPU",
                        "l2": "operands (768 MiB with C) exceed the 126 MB L2; no explicit flush",
+                       **({"library_options": list(args.ttb_option)} if args.ttb_option else {}),
                        "kernel": variant, "arithmetic": ("split precision on tcgen05: TF32 product of the high parts + two bf16 "
                                       "correction products, fp32 accumulate in TMEM chunks, fp32 register sums")},
             "clocks": clocks,
@@ -641,6 +645,8 @@ def main():
                          "are the callers either side of the path (bench_callers.py)")
     ap.add_argument("--skip-other-configs", action="store_true",
                     help="c4 only: leave the other BASELINE configurations out of the line")
+    ap.add_argument("--ttb-option", action="append", default=[], metavar="KEY=VALUE",
+                    help="library option set before anything runs (ttb_set_option), for A/B runs; repeatable")
     ap.add_argument("--deadline", type=float, default=900.0,
                     help="seconds after which the process ends itself, naming the phase it was in")
     args = ap.parse_args()

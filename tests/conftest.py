@@ -40,5 +40,5 @@ def reset_options(ttb):
     yield
     for key, value in (("force_variant", 0), ("tf32_terms", 2), ("k_chunk", 0), ("splitk", 1), ("two_cta", -1),
                        ("mask_big", 0), ("tc_debug", 0), ("tc_profile", 0), ("streamk", -1),
-                       ("conv_columns_mb", 2048), ("int_tensor", 1), ("peer_tma", 1), ("a_tmem", 0), ("extra_conv", 1), ("pieces", -1)):
+                       ("conv_columns_mb", 2048), ("int_tensor", 1), ("peer_tma", 1), ("a_tmem", 0), ("extra_conv", 1), ("pieces", -1), ("sk_pair", -1)):
         ttb.set_option(key, value)

@@ -336,3 +336,26 @@ def test_piece_schedule_meets_f32_tolerance_and_is_repeatable(forced, shape, pie
         forced.check_device(0)
     finally:
         forced.set_option("pieces", -1)
+
+
+@pytest.mark.parametrize("shape", [(1, 2048, 4096, 1024), (1, 3000, 2048, 2900), (2, 1100, 1536, 900)])
+def test_paired_stream_k_meets_f32_tolerance_and_is_repeatable(forced, shape):
+    """Paired stream-K (odd units walk their K-block range backwards; the two units that share a
+    tile draw tickets, the second adds the first's sums to its own and stores): same tolerance as
+    the plain cut, and the same bits on every run whichever unit comes second."""
+    rng = np.random.default_rng(92)
+    B, N, K, M = shape
+    a = dev(rng.standard_normal((B, N, K)).astype(np.float32))
+    b = dev(rng.standard_normal((B, K, M)).astype(np.float32))
+    want = np.matmul(host(a).astype(np.float64), host(b).astype(np.float64))
+    forced.set_option("streamk", 1)
+    forced.set_option("sk_pair", 1)
+    try:
+        first = host(forced.batched_matmul(a, b))
+        assert rel_to_max(first, want) <= F32_TOL
+        for _ in range(3):
+            assert np.array_equal(first, host(forced.batched_matmul(a, b)))
+        forced.check_device(0)
+    finally:
+        forced.set_option("streamk", -1)
+        forced.set_option("sk_pair", -1)

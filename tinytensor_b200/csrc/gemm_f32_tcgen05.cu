@@ -146,6 +146,15 @@ struct alignas(64) TcArgs {
     // ticket adds all parts in part order (its own included, read back, so that the result does
     // not depend on which part came last), lowers their flags and stores the tile.
     int pieces, pieces_log2, piece_len;
+    // Paired stream-K (sk_pair, with streamk): odd units walk their K-block range backwards, so a
+    // tile shared by an even unit and the odd one after it is finished by both at the END of
+    // their runs (one completion for two units) and a tile shared by an odd unit and the even one
+    // after it at the START.  Half as many tiles complete at the very end of the kernel, which is
+    // what the fused all-gather cannot hide.  Neither side knows which comes second, so both
+    // write their sums (the two slots of a unit: 0 for a tail, 1 for a head) and draw a ticket
+    // of the tile; the second adds the first's sums to its own (a + b = b + a: deterministic)
+    // and stores.  Needs every range to be at least one tile long (two contributors per tile).
+    int sk_pair;
     unsigned int *sk_tickets;  // arrival counters, one per tile, CTA and epilogue warp; 0 between launches
     int n_peers;   // fused all-gather: number of peer GPUs that receive every tile
     float *mc_c;   // fused all-gather through an NVLink multicast address of C (same offset and strides
@@ -461,6 +470,16 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                 seg_kb1_s[n] = k0 + (stop - pos);
                 ++n;
                 pos = stop;
+            }
+            if (args.sk_pair && (u & 1)) {
+                // odd unit: the cut range back to front
+                int first = 0;
+                while (first < n && seg_tile_s[first] < args.sk_tile0) ++first;
+                for (int a = first, b = n - 1; a < b; ++a, --b) {
+                    int x = seg_tile_s[a]; seg_tile_s[a] = seg_tile_s[b]; seg_tile_s[b] = x;
+                    x = seg_kb0_s[a]; seg_kb0_s[a] = seg_kb0_s[b]; seg_kb0_s[b] = x;
+                    x = seg_kb1_s[a]; seg_kb1_s[a] = seg_kb1_s[b]; seg_kb1_s[b] = x;
+                }
             }
             seg_count_s = n;
         }
@@ -998,6 +1017,42 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     if (lane == 0) args.sk_flags[slot] = 0u;  // consumed
                 }
                 if (lane == 0) args.sk_tickets[tk] = 0u;  // ready for the next launch
+            } else if (args.sk_pair && (kb0 != 0 || kb1 != num_kb)) {
+                // Paired stream-K: this unit holds one end of the tile, a neighbour the other.
+                const int which = kb0 != 0 ? 0 : 1;   // tail : head
+                const long long my_slot =
+                    ((static_cast<long long>(unit) * 2 + which) * CG + cta_rank) * EPI_WARPS + epi_warp;
+                float4 *dst = reinterpret_cast<float4 *>(args.sk_partials + my_slot * 4096) + lane;
+#pragma unroll
+                for (int q = 0; q < 32; ++q)
+                    dst[q * 32] = make_float4(sum[4 * q], sum[4 * q + 1], sum[4 * q + 2], sum[4 * q + 3]);
+                __threadfence();
+                __syncwarp();
+                unsigned int ticket = 0;
+                const long long tk = (static_cast<long long>(t) * CG + cta_rank) * EPI_WARPS + epi_warp;
+                if (lane == 0) ticket = atomicAdd(&args.sk_tickets[tk], 1u);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket == 0u) continue;           // first of the two: the other one stores
+                __threadfence();
+                const int other = which ? unit + 1 : unit - 1;
+                const long long slot =
+                    ((static_cast<long long>(other) * 2 + (which ^ 1)) * CG + cta_rank) * EPI_WARPS + epi_warp;
+                const float4 *src = reinterpret_cast<const float4 *>(args.sk_partials + slot * 4096) + lane;
+#pragma unroll
+                for (int v0 = 0; v0 < 32; v0 += 8) {
+                    float4 pv[8];
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) pv[v] = __ldcg(src + (v0 + v) * 32);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        sum[4 * (v0 + v)] += pv[v].x;
+                        sum[4 * (v0 + v) + 1] += pv[v].y;
+                        sum[4 * (v0 + v) + 2] += pv[v].z;
+                        sum[4 * (v0 + v) + 3] += pv[v].w;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) args.sk_tickets[tk] = 0u;  // ready for the next launch
             } else if (kb0 != 0) {
                 // Stream-K, a range that starts inside a tile: hand the partial sums to the unit
                 // that owns the tile.  Warp w of the owner reads exactly what warp w wrote here
@@ -1478,7 +1533,7 @@ bool plan(const Problem &p, TcPlan *pl, char *why, int why_len) {
 }
 
 template <int CG>
-int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt, int pieces_opt) {
+int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt, int pieces_opt, int pair_opt) {
     using C = Cfg<CG>;
     args.tiles_m = static_cast<int>((p.N + C::TILE_M - 1) / C::TILE_M);
     args.tiles_n = static_cast<int>((p.M + C::TILE_N - 1) / C::TILE_N);
@@ -1571,6 +1626,19 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt, int piec
     }
     args.streamk = streamk ? 1 : 0;
     if (!streamk && units > args.total_tiles) units = args.total_tiles;
+    // Paired stream-K (see TcArgs): halves the number of tiles that complete at the very end.
+    args.sk_pair = 0;
+    {
+        const bool sends = (args.n_peers > 0 && args.peer_tma) || args.mc_c != nullptr;
+        const bool fwd = args.n_peers > 0 && !args.peer_tma && args.mc_c == nullptr;  // counts its stores ahead
+        const bool want = pair_opt > 0;  // measured at 4 GPUs: no difference, so nothing selects it by itself
+        (void)sends;
+        if (streamk && want && !fwd && cut_kb_per_unit >= num_kb + 1 &&
+            static_cast<long long>(args.total_tiles) * CG * 8 <= kStreamKTickets) {
+            args.sk_pair = 1;
+            args.sk_tickets = args.sk_flags + static_cast<size_t>(sms) * 16;
+        }
+    }
     // Piece schedule instead (see TcArgs): wanted when tiles should complete all through the
     // kernel, i.e. with an all-gather fused into the product that the epilogue itself sends.
     args.pieces = 0;
@@ -1714,8 +1782,8 @@ int launch_f32_tcgen05(const Problem &p, const F32Options &opt, int n_peers, voi
     args.dbg = opt.dbg;
     int sms = 148;
     sm_count(p.device, &sms);
-    if (opt.two_cta) return launch_cg<2>(p, args, sms, opt.streamk, opt.pieces);
-    return launch_cg<1>(p, args, sms, opt.streamk, opt.pieces);
+    if (opt.two_cta) return launch_cg<2>(p, args, sms, opt.streamk, opt.pieces, opt.sk_pair);
+    return launch_cg<1>(p, args, sms, opt.streamk, opt.pieces, opt.sk_pair);
 }
 
 }  // namespace ttb

@@ -42,6 +42,7 @@ struct Options {
     int peer_tma = 1;            // fused all-gather: epilogue tensor stores reach the peers (0: forwarding warps)
     int a_tmem = 0;              // f32 hybrid split: correction MMAs read their A operands from tensor memory
     int extra_conv = 1;          // f32 pair form: warps 2-3 convert half of every B tile
+    int sk_pair = -1;            // f32 tensor-core kernel: paired stream-K (-1 automatic, 0 never, 1 whenever possible)
     int pieces = -1;             // f32 tensor-core kernel: piece schedule (-1 automatic, 0 never, n parts per tile)
 };
 Options g_opt;
@@ -421,6 +422,7 @@ static F32Options f32_options(bool two_cta) {
     o.a_tmem = g_opt.a_tmem;
     o.extra_conv = g_opt.extra_conv;
     o.pieces = g_opt.pieces;
+    o.sk_pair = g_opt.sk_pair;
     return o;
 }
 
@@ -911,6 +913,14 @@ TTB_API int ttb_set_option(const char *key, int64_t value) {
         g_opt.a_tmem = value != 0;
         return TTB_OK;
     }
+    if (!strcmp(key, "sk_pair")) {
+        if (value < -1 || value > 1) {
+            set_error("sk_pair takes -1 (automatic), 0 or 1");
+            return TTB_EINVAL;
+        }
+        g_opt.sk_pair = static_cast<int>(value);
+        return TTB_OK;
+    }
     if (!strcmp(key, "pieces")) {
         if (value < -1 || value > 64) {
             set_error("pieces out of range (-1 automatic, 0 never, up to 64 parts per tile)");
@@ -955,6 +965,7 @@ TTB_API int64_t ttb_get_option(const char *key) {
     if (!strcmp(key, "a_tmem")) return g_opt.a_tmem;
     if (!strcmp(key, "extra_conv")) return g_opt.extra_conv;
     if (!strcmp(key, "pieces")) return g_opt.pieces;
+    if (!strcmp(key, "sk_pair")) return g_opt.sk_pair;
     set_error("unknown option '%s'", key);
     return TTB_EINVAL;
 }
