@@ -370,7 +370,7 @@ TTB_API const char *ttb_variant_name(int variant);
  * "a_tmem" (0, default; 1: the f32 kernel's correction products read their A operands from
  * tensor memory, where the converters put them, instead of shared memory -- measured: no
  * faster, the pair form then has room for one accumulator only),
- * "extra_conv" (1, default: the two spare warps of the f32 pair kernel convert half of every
+ * "extra_conv" (1, default: the two spare warps of the f32 pair kernel convert 5/8 of every
  * rhs tile; 0: converter warpgroup only),
  * "sk_pair" (-1 / 0, default: off; 1 whenever stream-K cuts tiles and every
  * unit's range is a tile long: odd units walk their K-block range backwards and the two units

@@ -294,7 +294,7 @@ def test_converter_variants_meet_f32_tolerance_all_layouts(forced, shape, option
     `a_tmem` = 1 puts the A operands of the correction products into tensor memory (written by the
     converters with tcgen05.st, read by the MMAs in their A-from-TMEM form; the pair form then
     keeps one accumulator); `extra_conv` = 0 takes the two spare warps of the pair form out of the
-    conversion (the default has them convert half of every B tile)."""
+    conversion (the default has them convert 5/8 of every B tile)."""
     rng = np.random.default_rng(77)
     B, N, K, M = shape
     a = dev(rng.standard_normal((B, N, K)).astype(np.float32))

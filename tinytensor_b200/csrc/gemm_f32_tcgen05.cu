@@ -506,7 +506,7 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
     const int acc_bufs = (a_tmem && PAIR) ? 1 : 2;
     // The pair form has one converter warp per scheduler, and converting is what bounds the kernel;
     // its warps 2-3 have nothing to do unless they forward tiles to peers (the fallback form of the
-    // fused all-gather), so they convert the second half of every B tile.
+    // fused all-gather), so they convert 5/8 of every B tile.
     const bool extra_conv = PAIR && args.terms == 2 && args.extra_conv != 0;
     const uint32_t a_slot_col0 = static_cast<uint32_t>(acc_bufs * C::ACC_COLS);
 
@@ -821,11 +821,12 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
         __threadfence_system();
       } else if (extra_conv) {
         // ------------------------------------------------------------ extra converters (warps 2-3, pair form)
-        // Chunks [512, 1024) of every raw B tile: thread e takes 512 + e + 64 u, u = 0..7, which
-        // land 512 bytes apart in the bf16 tiles (see hybrid_dst).  Same waits and the same
-        // converted barrier as the converter warpgroup.
+        // Chunks [384, 1024) of every raw B tile: thread e takes 384 + e + 64 u, u = 0..9, which
+        // land 512 bytes apart in the bf16 tiles (see hybrid_dst); the converter warpgroup keeps
+        // the A tile and chunks [0, 384) of B, so its threads convert 11 chunks per K block and
+        // these 10.  Same waits and the same converted barrier as the converter warpgroup.
         const int etid = threadIdx.x - 64;  // 0..63
-        const int dst0 = hybrid_dst(512 + etid, args.b_mn_major != 0);
+        const int dst0 = hybrid_dst(384 + etid, args.b_mn_major != 0);
         const uint32_t conv_remote0 = PAIR ? mapa(smem_u32(&conv_bar[0]), 0) : 0u;
         int stage = 0, sstage = 0;
         uint32_t phase = 0, sphase = 0;
@@ -840,20 +841,20 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                     ok = false;
                     break;
                 }
-                const uint4 *rt = reinterpret_cast<const uint4 *>(tiles + stage * STAGE_BYTES + TILE_BYTES) + 512 + etid;
+                const uint4 *rt = reinterpret_cast<const uint4 *>(tiles + stage * STAGE_BYTES + TILE_BYTES) + 384 + etid;
                 uint8_t *s16 = tiles + SMALL_RING_OFFSET + sstage * STAGE_BYTES + 2 * H_TILE_BYTES;
                 uint8_t *x16 = s16 + H_TILE_BYTES;
 #pragma unroll
-                for (int b4 = 0; b4 < 8; b4 += 4) {
-                    uint4 x[4];
+                for (int b4 = 0; b4 < 10; b4 += 5) {
+                    uint4 x[5];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) x[u] = rt[(b4 + u) * 64];
+                    for (int u = 0; u < 5; ++u) x[u] = rt[(b4 + u) * 64];
                     float za = 0.0f, zb = 0.0f;
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) hybrid_chunk_unmasked(x[u], s16, x16, dst0 + (b4 + u) * 512, za, zb);
+                    for (int u = 0; u < 5; ++u) hybrid_chunk_unmasked(x[u], s16, x16, dst0 + (b4 + u) * 512, za, zb);
                     if (!all_finite(za, zb)) {
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) hybrid_chunk(x[u], s16, x16, dst0 + (b4 + u) * 512);
+                        for (int u = 0; u < 5; ++u) hybrid_chunk(x[u], s16, x16, dst0 + (b4 + u) * 512);
                     }
                 }
                 fence_proxy_async_smem();
@@ -1405,9 +1406,9 @@ __global__ void __launch_bounds__(Cfg<CG>::NUM_THREADS, 1) gemm_f32_3xtf32_kerne
                         const uint4 *rt = reinterpret_cast<const uint4 *>(raw_b + half * TILE_BYTES);
                         uint8_t *s16 = out_b + half * 2 * H_TILE_BYTES;
                         uint8_t *x16 = s16 + H_TILE_BYTES;
-                        // With the extra converter warps at work (pair form), they take the second
-                        // half of the B tile's chunks.
-                        const int n_here = (half == 1 && extra_conv) ? PER_T / 2 : PER_T;
+                        // With the extra converter warps at work (pair form), they take chunks
+                        // [384, 1024) of the B tile.
+                        const int n_here = (half == 1 && extra_conv) ? 3 : PER_T;
                         uint4 x[PER_T];
 #pragma unroll
                         for (int u = 0; u < PER_T; ++u)

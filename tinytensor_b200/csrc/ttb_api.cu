@@ -41,7 +41,7 @@ struct Options {
     int int_tensor = 1;          // i32 products may use the int8 tensor-core kernel
     int peer_tma = 1;            // fused all-gather: epilogue tensor stores reach the peers (0: forwarding warps)
     int a_tmem = 0;              // f32 hybrid split: correction MMAs read their A operands from tensor memory
-    int extra_conv = 1;          // f32 pair form: warps 2-3 convert half of every B tile
+    int extra_conv = 1;          // f32 pair form: warps 2-3 convert 5/8 of every B tile
     int sk_pair = -1;            // f32 tensor-core kernel: paired stream-K (-1 automatic, 0 never, 1 whenever possible)
     int pieces = -1;             // f32 tensor-core kernel: piece schedule (-1 automatic, 0 never, n parts per tile)
 };
