@@ -598,7 +598,7 @@ def run_ours(args):
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                          "traffic": None,
                          "traffic_source": "not measured in this run; one ncu capture of this kernel on this workload is "
-                                           "summarised in profiles/gemm_f32_3xtf32_pair_8192cubed.md (2.72 GB per full launch)",
+                                           "summarised in profiles/gemm_f32_3xtf32_pair_8192cubed.md (2.58 GB per full launch)",
                          "kernel_ms": kernel_ms,
                          "peak_source": f"{peak_kind}: bf16 burst {burst} TFLOP/s / 4 (one TF32 + two bf16 products per "
                                         "flop); the timed loop lasts well under a second",
