@@ -283,11 +283,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && leader) {
             const uint32_t idesc = make_idesc_u8(BM * CG, BN);
-            uint32_t peer_plane_empty[PLANE_STAGES] = {0, 0}, peer_acc_full = 0;
-            if constexpr (PAIR) {
-                for (int s = 0; s < PLANE_STAGES; ++s) peer_plane_empty[s] = mapa(smem_u32(&plane_empty_bar[s]), 1);
-                peer_acc_full = mapa(smem_u32(&acc_full_bar), 1);
-            }
             int ps = 0;
             uint32_t pphase = 0;
             uint32_t acc_phase = 0;
@@ -326,16 +321,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i32_limb_kernel(const __g
                                 mma_i8(tmem_base + static_cast<uint32_t>(s * BN), da, db, idesc, ia == 0 ? fresh : 1u);
                         }
                     }
-                    mma_commit<CG>(smem_u32(&plane_empty_bar[ps]));
-                    if constexpr (PAIR) mma_commit<CG>(peer_plane_empty[ps]);
+                    // (one arrival per barrier reaches both CTAs of a pair)
+                    if constexpr (PAIR)
+                        mma_commit_both(smem_u32(&plane_empty_bar[ps]));
+                    else
+                        mma_commit<CG>(smem_u32(&plane_empty_bar[ps]));
                     if (++ps == PLANE_STAGES) {
                         ps = 0;
                         pphase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                mma_commit<CG>(smem_u32(&acc_full_bar));
-                if constexpr (PAIR) mma_commit<CG>(peer_acc_full);
+                if constexpr (PAIR)
+                    mma_commit_both(smem_u32(&acc_full_bar));
+                else
+                    mma_commit<CG>(smem_u32(&acc_full_bar));
                 acc_phase ^= 1u;
             }
             // Everything issued must have retired before TMEM is freed.
