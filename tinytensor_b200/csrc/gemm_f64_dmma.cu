@@ -6,8 +6,9 @@
 // (tinytensor/tensor/backend/cuda/kernel/matmul.cuh:74,131 accumulate in T).
 // Replaces matmul_kernel<double> of the reference.
 //
-// One CTA: 128 x 128 output tile, 8 warps as 2 (rows) x 4 (columns), each warp a
-// 64 x 32 tile = 4 x 4 MMA tiles of 16 x 8, accumulators in registers.  K runs in
+// One CTA: 128 x 64 output tile, 4 warps as 2 (rows) x 2 (columns), each warp a
+// 64 x 32 tile = 4 x 4 MMA tiles of 16 x 8, accumulators in registers; two CTAs per SM, so that
+// one keeps the DMMA pipe busy while the other sits at its per-K-block barrier.  K runs in
 // blocks of 8, staged in shared memory as [k][row] for both operands (lhs is stored
 // transposed) with a row pitch of tile+4 doubles, which makes every fragment read
 // conflict-free.  Global loads go through registers (prefetch of the next block while
@@ -18,10 +19,11 @@
 namespace ttb {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 8;
+constexpr int BM = 128, BN = 64, BK = 8;
 constexpr int PITCH_A = BM + 4, PITCH_B = BN + 4;
-constexpr int THREADS = 256;
+constexpr int THREADS = 128;
 constexpr int WM = 64, WN = 32;  // warp tile
+constexpr int WARPS_N = BN / WN; // warps side by side along the columns
 constexpr int MT = WM / 16, NT = WN / 8;
 
 struct DmmaArgs {
@@ -42,15 +44,15 @@ __device__ __forceinline__ void dmma_m16n8k4(double (&c)[4], double a0, double a
         : "d"(a0), "d"(a1), "d"(b0));
 }
 
-__global__ void __launch_bounds__(THREADS) gemm_f64_dmma_kernel(DmmaArgs p) {
+__global__ void __launch_bounds__(THREADS, 2) gemm_f64_dmma_kernel(DmmaArgs p) {
     __shared__ __align__(16) double As[2][BK][PITCH_A];
     __shared__ __align__(16) double Bs[2][BK][PITCH_B];
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;  // MMA fragment coordinates
-    const int wm = (warp >> 2) * WM;        // warp's row offset in the CTA tile
-    const int wn = (warp & 3) * WN;
+    const int wm = (warp / WARPS_N) * WM;   // warp's row offset in the CTA tile
+    const int wn = (warp % WARPS_N) * WN;
     const long long m0 = static_cast<long long>(blockIdx.y) * BM;
     const long long n0 = static_cast<long long>(blockIdx.x) * BN;
     const long long batch = blockIdx.z;
@@ -61,12 +63,12 @@ __global__ void __launch_bounds__(THREADS) gemm_f64_dmma_kernel(DmmaArgs p) {
     // Loading threads walk the dim with the smaller stride fastest.
     const bool a_k_fast = p.a_sk <= p.a_si;
     const bool b_j_fast = p.b_sj <= p.b_sk;
-    constexpr int ELEMS = BM * BK / THREADS;  // 4 per operand per thread
-    double ra[ELEMS], rb[ELEMS];
+    constexpr int ELEMS_A = BM * BK / THREADS, ELEMS_B = BN * BK / THREADS;  // 8 and 4 per thread
+    double ra[ELEMS_A], rb[ELEMS_B];
 
     auto load_global = [&](long long k0) {
 #pragma unroll
-        for (int l = 0; l < ELEMS; ++l) {
+        for (int l = 0; l < ELEMS_A; ++l) {
             const int idx = tid + l * THREADS;
             const int kk = a_k_fast ? idx % BK : idx / BM;
             const int r = a_k_fast ? idx / BK : idx % BM;
@@ -74,7 +76,7 @@ __global__ void __launch_bounds__(THREADS) gemm_f64_dmma_kernel(DmmaArgs p) {
             ra[l] = (gi < p.N && gk < p.K) ? a[gi * p.a_si + gk * p.a_sk] : 0.0;
         }
 #pragma unroll
-        for (int l = 0; l < ELEMS; ++l) {
+        for (int l = 0; l < ELEMS_B; ++l) {
             const int idx = tid + l * THREADS;
             const int kk = b_j_fast ? idx / BN : idx % BK;
             const int j = b_j_fast ? idx % BN : idx / BK;
@@ -84,14 +86,14 @@ __global__ void __launch_bounds__(THREADS) gemm_f64_dmma_kernel(DmmaArgs p) {
     };
     auto store_shared = [&](int buf) {
 #pragma unroll
-        for (int l = 0; l < ELEMS; ++l) {
+        for (int l = 0; l < ELEMS_A; ++l) {
             const int idx = tid + l * THREADS;
             const int kk = a_k_fast ? idx % BK : idx / BM;
             const int r = a_k_fast ? idx / BK : idx % BM;
             As[buf][kk][r] = ra[l];
         }
 #pragma unroll
-        for (int l = 0; l < ELEMS; ++l) {
+        for (int l = 0; l < ELEMS_B; ++l) {
             const int idx = tid + l * THREADS;
             const int kk = b_j_fast ? idx / BN : idx % BK;
             const int j = b_j_fast ? idx % BN : idx / BK;
@@ -176,7 +178,8 @@ __global__ void __launch_bounds__(THREADS) gemm_f64_dmma_kernel(DmmaArgs p) {
 // The FP64 tensor-core rate itself: every warp keeps the GEMM kernel's 16 independent 16 x 8
 // accumulator tiles in registers and issues m16n8k4 MMAs on register operands, with no memory
 // traffic.  What this loop reaches is the ceiling the GEMM kernel's roofline is quoted against.
-__global__ void __launch_bounds__(THREADS) dmma_peak_kernel(double *sink, int iters, double a_seed, double b_seed) {
+constexpr int PEAK_THREADS = 256;
+__global__ void __launch_bounds__(PEAK_THREADS) dmma_peak_kernel(double *sink, int iters, double a_seed, double b_seed) {
     double acc[MT * NT][4];
 #pragma unroll
     for (int j = 0; j < MT * NT; ++j)
@@ -212,11 +215,11 @@ int measure_fp64_tensor_peak(int device, double *tflops) {
     cudaEventCreate(&t1);
     const int iters = 1 << 14;
     const int ctas = 2 * sms;
-    const double flop = 2.0 * 16 * 8 * 4 * (MT * NT) * static_cast<double>(iters) * (THREADS / 32) * ctas;
+    const double flop = 2.0 * 16 * 8 * 4 * (MT * NT) * static_cast<double>(iters) * (PEAK_THREADS / 32) * ctas;
     double best = 0.0;
     for (int rep = 0; rep < 4 && e == cudaSuccess; ++rep) {  // the first launch is the warm-up
         cudaEventRecord(t0, nullptr);
-        dmma_peak_kernel<<<ctas, THREADS>>>(sink, iters, 1.0000001, 0.9999999);
+        dmma_peak_kernel<<<ctas, PEAK_THREADS>>>(sink, iters, 1.0000001, 0.9999999);
         cudaEventRecord(t1, nullptr);
         e = cudaEventSynchronize(t1);
         float ms = 0.f;
