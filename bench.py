@@ -270,6 +270,18 @@ def progress(msg: str) -> None:
           flush=True)
 
 
+def sustained_step_count(ms_per_step: float, steps: int, torch, dist=None, device=None) -> int:
+    """Steps of the >= 2 s loop, from the measured time of one step.  Every rank must come out with
+    the SAME number: each step meets the other ranks at a barrier, and a rank with one step more
+    would wait there for ever.  So the slowest rank's time decides (all-reduce MAX)."""
+    ms_all = ms_per_step
+    if dist is not None:
+        t = torch.tensor([ms_per_step], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_all = float(t.item())
+    return int(max(steps, min(4000, 2200.0 / max(ms_all, 1e-3))))
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -372,13 +384,7 @@ def run_ours(args):
     ttb.check_device(local_rank)
 
     # The same step for at least two seconds without a pause: the power-capped regime.
-    # (the step count must be the same on every rank: each step meets the other ranks at a barrier)
-    ms_all = ms_per_step
-    if world > 1:
-        t = torch.tensor([ms_per_step], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_all = float(t.item())
-    sustained_steps = int(max(args.steps, min(4000, 2200.0 / max(ms_all, 1e-3))))
+    sustained_steps = sustained_step_count(ms_per_step, args.steps, torch, dist if world > 1 else None, dev)
     sus_ms, _, sus_clocks = timed_loop(sustained_steps, False)
     progress(f"sustained loop done: {sus_ms:.3f} ms per step over {sustained_steps} steps")
     ttb.check_device(local_rank)
