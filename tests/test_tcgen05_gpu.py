@@ -359,3 +359,32 @@ def test_paired_stream_k_meets_f32_tolerance_and_is_repeatable(forced, shape):
     finally:
         forced.set_option("streamk", -1)
         forced.set_option("sk_pair", -1)
+
+
+@pytest.mark.parametrize("level", [1, 2])
+def test_profile_counters_do_not_change_results(forced, level):
+    """`tc_profile` = 1 runs the instantiation with cycle counters in every role's loop, 2 records
+    CTA lifetimes only: same bits as the plain kernel, and counters that make sense (a lifetime
+    for every CTA that ran; with level 1 the converters' busy time inside it)."""
+    import ctypes
+
+    rng = np.random.default_rng(93)
+    a = dev(rng.standard_normal((1, 1024, 2048)).astype(np.float32))
+    b = dev(rng.standard_normal((1, 2048, 768)).astype(np.float32))
+    plain = host(forced.batched_matmul(a, b))
+    forced.set_option("tc_profile", level)
+    try:
+        got = host(forced.batched_matmul(a, b))
+        torch.cuda.synchronize()
+        out = (ctypes.c_int64 * (148 * 8))()
+        assert forced.lib().ttb_tc_profile(0, out, 148) == 0
+        prof = np.array(out[:], dtype=np.int64).reshape(148, 8)
+    finally:
+        forced.set_option("tc_profile", 0)
+    assert np.array_equal(plain, got)
+    total = prof[:, 7]
+    assert total.max() > 0
+    if level == 1:
+        busy = prof[:, 5]
+        assert busy.max() > 0 and np.all(busy <= total.max())
+    forced.check_device(0)
