@@ -372,11 +372,11 @@ TTB_API const char *ttb_variant_name(int variant);
  * faster, the pair form then has room for one accumulator only),
  * "extra_conv" (1, default: the two spare warps of the f32 pair kernel convert 5/8 of every
  * rhs tile; 0: converter warpgroup only),
- * "sk_pair" (-1 / 0, default: off; 1 whenever stream-K cuts tiles and every
+ * "sk_pair" (-1, default: with a fused all-gather; 0 never; 1 whenever stream-K cuts tiles and every
  * unit's range is a tile long: odd units walk their K-block range backwards and the two units
  * that share a tile settle by ticket which of them adds the other's sums and stores, so half
- * as many tiles complete at the very end of the kernel -- measured with the fused all-gather at
- * 4 GPUs: no difference in the step time),
+ * as many tiles complete at the very end of the kernel, where the fused all-gather has nothing
+ * left to hide their exchange behind -- measured at 8 GPUs: 0.568 instead of 0.671 ms per step),
  * "pieces" (-1 / 0, default: off; n >= 2: the f32 tensor-core kernel cuts every tile's K range into
  * the largest power of two of equal parts not above n and deals the parts out round-robin, so
  * that tiles complete all through the kernel; the part that arrives last adds all parts in part

@@ -87,8 +87,8 @@ struct F32Options {
     int peer_tma = 1;   // fused all-gather: peers are reached by the epilogue's bulk tensor stores when possible
     int a_tmem = 0;     // hybrid split: A operands of the correction MMAs in tensor memory
     int extra_conv = 1; // pair form: the two spare warps of the producer warpgroup convert too
-    int sk_pair = -1;   // paired stream-K (odd units walk their range backwards, tickets): -1 / 0 = off,
-                        // 1 = whenever stream-K allows
+    int sk_pair = -1;   // paired stream-K (odd units walk their range backwards, tickets): -1 = with a fused
+                        // all-gather that the epilogue sends, 0 = never, 1 = whenever stream-K allows
     int pieces = -1;    // piece schedule (every tile's K cut into this many parts, dealt out round-robin):
                         // -1 = four parts when an all-gather is fused into the product, 0 = never
 };

@@ -1632,8 +1632,7 @@ int launch_cg(const Problem &p, TcArgs &args, int sms, int streamk_opt, int piec
     {
         const bool sends = (args.n_peers > 0 && args.peer_tma) || args.mc_c != nullptr;
         const bool fwd = args.n_peers > 0 && !args.peer_tma && args.mc_c == nullptr;  // counts its stores ahead
-        const bool want = pair_opt > 0;  // measured at 4 GPUs: no difference, so nothing selects it by itself
-        (void)sends;
+        const bool want = pair_opt < 0 ? sends : pair_opt != 0;
         if (streamk && want && !fwd && cut_kb_per_unit >= num_kb + 1 &&
             static_cast<long long>(args.total_tiles) * CG * 8 <= kStreamKTickets) {
             args.sk_pair = 1;
