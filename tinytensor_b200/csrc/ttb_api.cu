@@ -990,9 +990,9 @@ TTB_API int ttb_check_device(int device_id) {
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
     if (h.error != 0) {
         cudaMemset(d->status, 0, sizeof(DeviceStatus));
-        // A kernel that gave up may have left stream-K flags raised: lower them all.
+        // A kernel that gave up may have left stream-K flags raised or tickets drawn: clear them all.
         for (int i = 0; i < d->sk_count; ++i)
-            cudaMemset(d->sk[i].flags, 0, static_cast<size_t>(d->sms) * 8 * sizeof(unsigned int));
+            cudaMemset(d->sk[i].flags, 0, (static_cast<size_t>(d->sms) * 16 + kStreamKTickets) * sizeof(unsigned int));
         set_error("device %d: a bounded wait inside a kernel gave up (code %u, detail %u)", device_id, h.error,
                   h.detail);
         return TTB_ETIMEOUT;
