@@ -43,8 +43,11 @@ def _worker(rank, world, port, q):
         # column blocks: f32 (fused and NCCL exchange), ragged sizes included
         # "many_tiles": every CTA pair works through several tiles, so the tile-by-tile forwarding and
         # the jointly forwarded last tile are both exercised
+        # "paired": at two ranks a block of 100 pair tiles with 128 K blocks each -- every tile is cut
+        # and every unit's range is longer than a tile, so the fused kernel pairs its units (odd ones
+        # walk their range backwards, the two that share a tile settle by ticket which one stores)
         for name, (n, k, m) in {"square": (1024, 512, 1024), "ragged": (1000, 520, 1300),
-                                "many_tiles": (4096, 256, 8192)}.items():
+                                "many_tiles": (4096, 256, 8192), "paired": (2560, 4096, 5120)}.items():
             A = torch.randn((1, n, k), generator=g, device=dev)
             B = torch.randn((1, k, m), generator=g, device=dev)
             full = ttb.batched_matmul(A, B)
