@@ -25,10 +25,14 @@
 //   warp 0       TMA producer: cp.async.bulk.tensor loads of the raw fp32 A and B tiles
 //                through tensor maps built from the operand's own strides (K-major or
 //                MN-major, so transposed views need no copy);
-//   warp 1       MMA issuer: one thread issues the tcgen05.mma instructions of a K block (TF32
-//                on the raw tiles, then the corrections), accumulating in TMEM;
-//                tcgen05.commit releases the stage / publishes the accumulator.
-//   warps 2-3    idle, or (fused all-gather) forward finished tiles to the peer GPUs' C.
+//   warp 1       MMA issuer: one thread issues the tcgen05.mma instructions of a K block,
+//                accumulating in TMEM: in the hybrid form the two corrections first, a
+//                tcgen05.commit that releases the correction slot, then the TF32 product of the
+//                raw tiles and the commit that releases the raw slot -- the converters' round
+//                trip (slot free -> convert -> converted -> issue) runs behind the TF32 product.
+//                A commit reaches the barrier of both CTAs of a pair (its multicast form).
+//   warps 2-3    pair form: convert 5/8 of every B tile; or, in the fallback form of the fused
+//                all-gather, forward finished tiles to the peer GPUs' C; idle in the one-CTA form.
 //   epilogue WG  (one per 128 accumulator columns): tcgen05.ld each chunk sum, add into
 //                registers, store C after the last chunk.  Two TMEM accumulators, so the
 //                read-out of chunk i overlaps the MMAs of chunk i+1.
