@@ -46,3 +46,27 @@ def test_k_major_chunk_keeps_its_row_and_k_range():
             chunk16, within = logical // 16 % 4, logical % 16
             swizzled = r * 64 + ((chunk16 ^ ((r >> 1) & 3)) * 16) + within
             assert dst_offset(r * 8 + cp, False) == swizzled
+
+
+@pytest.mark.parametrize("mn_major", [False, True])
+def test_split_of_the_rhs_tile_between_warpgroup_and_spare_warps(mn_major):
+    """Pair form: the converter warpgroup (128 threads) takes chunks [0, 384) of the B tile, thread
+    t its chunks t + 128 u (u < 3); the two spare warps (64 threads) take [384, 1024), thread e its
+    chunks 384 + e + 64 u (u < 10), 512 bytes apart in the bf16 tile.  Together: every chunk once,
+    every destination once, and the spare warps' constant step holds across box boundaries."""
+    seen, dsts = [], []
+    for t in range(128):
+        for u in range(3):
+            ci = t + 128 * u
+            seen.append(ci)
+            dsts.append(dst_offset(t, mn_major) + u * 128 * 8)
+            assert dsts[-1] == dst_offset(ci, mn_major)
+    for e in range(64):
+        first = dst_offset(384 + e, mn_major)
+        for u in range(10):
+            ci = 384 + e + 64 * u
+            seen.append(ci)
+            dsts.append(first + u * 512)
+            assert dsts[-1] == dst_offset(ci, mn_major)
+    assert sorted(seen) == list(range(1024))
+    assert sorted(dsts) == list(range(0, 8192, 8))
